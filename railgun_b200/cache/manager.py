@@ -42,6 +42,7 @@ class PagedKVNeed:
     num_kv_heads: int
     head_dim: int
     window: int = 0            # 0: all keys are kept
+    keep_first: int = 0        # with a window: the first positions that every later query still sees
     page_size: int = 0         # 0: the engine's
     pool_tokens: int = 0       # 0: the engine's
     dtype: str | None = None   # None: the model's
@@ -79,6 +80,7 @@ def _lib():
         lib.rg_cache_create.argtypes = [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]
         lib.rg_cache_destroy.argtypes = [c_void_p]
         lib.rg_cache_destroy.restype = None
+        lib.rg_cache_set_keep_first.argtypes = [c_void_p, c_int, c_int]
         for name in ("add_request", "release", "has", "num_computed", "slot"):
             getattr(lib, f"rg_cache_{name}").argtypes = [c_void_p, c_longlong]
         for name in ("reserve", "commit"):
@@ -138,7 +140,7 @@ class PageAllocator:
     """The C++ cache manager: page groups, block tables, state slots and the slots' request records.  No
     device memory."""
 
-    def __init__(self, page_sizes, num_pages, windows, max_requests: int):
+    def __init__(self, page_sizes, num_pages, windows, max_requests: int, keep_first=None):
         self._lib = _lib()
         n = len(page_sizes)
         if not (len(num_pages) == len(windows) == n):
@@ -152,6 +154,11 @@ class PageAllocator:
         self.num_pages = [int(x) for x in num_pages]
         self.windows = [int(x) for x in windows]
         self.max_requests = int(max_requests)
+        # windowed groups whose queries also see their request's first tokens keep those tokens' pages
+        self.keep_first = [int(x) for x in (keep_first or [0] * n)]
+        for g, keep in enumerate(self.keep_first):
+            if keep and self._lib.rg_cache_set_keep_first(self._h, g, keep):
+                raise CacheError(f"group {g}: cannot keep the first {keep} positions")
         self._buf = np.empty(64, dtype=np.int32)
         self._any_sampled = c_int(0)
         if self._lib.rg_cache_record_bytes() != REQUEST_RECORD.itemsize:
@@ -363,7 +370,8 @@ class CacheManager:
                 raise CacheError(f"a page must hold at least one token, not {ps}")
             self.groups.append(GroupInfo(need, ps, (int(need.pool_tokens or max_tokens) + ps - 1) // ps, cids))
         self.alloc = PageAllocator([g.page_size for g in self.groups], [g.num_pages for g in self.groups],
-                                   [g.need.window for g in self.groups], max_requests)
+                                   [g.need.window for g in self.groups], max_requests,
+                                   keep_first=[g.need.keep_first for g in self.groups])
         self.max_requests = int(max_requests)
         self.dtype = dtype
         self.device = device

@@ -88,6 +88,15 @@ class KeyReader:
             return tuple(v)
         raise ConfigError(f"{self.where}: '{key}' must be an integer or a list of integers, got {v!r}")
 
+    def number_list(self, key: str, default: Any = _MISSING):
+        """A list of numbers, returned as a tuple of floats."""
+        v = self._get(key, default)
+        if v is _MISSING:
+            return default
+        if isinstance(v, list) and all(isinstance(t, (int, float)) and not isinstance(t, bool) for t in v):
+            return tuple(float(t) for t in v)
+        raise ConfigError(f"{self.where}: '{key}' must be a list of numbers, got {v!r}")
+
     def obj(self, key: str):
         """A nested object as a KeyReader, or None when absent or null."""
         v = self.data.get(key)

@@ -76,3 +76,5 @@ def _ensure_builtin():
         from ..models import dizatar  # noqa: F401
     if "Rupulix" not in _ARCHITECTURES:
         from ..models import rupulix  # noqa: F401
+    if "Mepatar" not in _ARCHITECTURES:
+        from ..models import mepatar  # noqa: F401

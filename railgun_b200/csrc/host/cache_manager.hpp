@@ -4,7 +4,9 @@
 // has its own pages, its own free list and, for every request, its own block
 // table.  A group with a window w only needs the keys of the last w positions:
 // pages that every future query has passed are given back at commit time and
-// their block-table entries become -1.  Beside the pages, every live request
+// their block-table entries become -1 (except the pages that hold any of the
+// group's first keep_first positions, which a window that keeps the first
+// tokens goes on reading).  Beside the pages, every live request
 // holds one state slot: an index into fixed-size per-request buffers, and the
 // place of its RequestRecord, the one fixed-size description of a live request
 // (position, lengths, sampling parameters, seed) that decode steps are packed
@@ -39,6 +41,7 @@ struct CacheGroup {
     int page_size = 16;
     int num_pages = 0;
     int window = 0;                 // 0: every key is kept
+    int keep_first = 0;             // with a window: the first positions that stay visible, so their pages stay
     std::deque<int> free_list;
     std::vector<int> refcount;
 };
@@ -84,6 +87,12 @@ public:
 
     int num_groups() const { return (int)groups_.size(); }
     const CacheGroup& group(int g) const { return groups_[g]; }
+    // A windowed group whose queries also see the first `keep` positions: their pages are not given back.
+    int set_keep_first(int g, int keep) {
+        if (g < 0 || g >= (int)groups_.size() || keep < 0 || !reqs_.empty()) return CACHE_BAD_ARGUMENT;
+        groups_[g].keep_first = keep;
+        return CACHE_OK;
+    }
     int free_pages(int g) const { return (int)groups_[g].free_list.size(); }
     int free_slots() const { return (int)free_slots_.size(); }
     int max_slots() const { return max_slots_; }
@@ -174,6 +183,7 @@ public:
             const int first_needed = new_len - G.window + 1;     // lowest key any later query reads
             for (size_t i = 0; i < r.tables[g].size(); ++i) {
                 if ((int)(i + 1) * G.page_size > first_needed) break;
+                if ((int)i * G.page_size < G.keep_first) continue;
                 if (r.tables[g][i] >= 0) {
                     const int st = free_page(G, r.tables[g][i]);
                     if (st != CACHE_OK) return st;

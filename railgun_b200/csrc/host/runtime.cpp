@@ -21,6 +21,7 @@ void* rg_cache_create(int n_groups, const int* page_size, const int* num_pages, 
     try { return new CacheManager(n_groups, page_size, num_pages, window, max_slots); } catch (...) { return nullptr; }
 }
 void rg_cache_destroy(void* h) { delete (CacheManager*)h; }
+int rg_cache_set_keep_first(void* h, int group, int keep) { RG_GUARD(return ((CacheManager*)h)->set_keep_first(group, keep)) }
 int rg_cache_add_request(void* h, long long id) { RG_GUARD(return ((CacheManager*)h)->add_request(id)) }
 int rg_cache_reserve(void* h, long long id, int new_len) { RG_GUARD(return ((CacheManager*)h)->reserve(id, new_len)) }
 int rg_cache_can_reserve(void* h, long long id, int new_len, int spare) {

@@ -174,3 +174,31 @@ extern "C" int rg_activation(const void* in, void* out, int dtype, int kind, lon
                          (size_t)n);
     return RG_ERR_UNSUPPORTED;
 }
+
+// [T, 2 I] = gate | up  ->  [T, I] = act(gate) * up, for the gated activations of common.cuh (gated_act).
+template <typename A>
+__global__ void gated_activation_kernel(const A* __restrict__ gu, A* __restrict__ out, int I, int kind, float limit,
+                                        size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / I, i = idx - t * I;
+    out[idx] = from_f32<A>(gated_act(to_f32(gu[t * 2 * I + i]), to_f32(gu[t * 2 * I + I + i]), kind, limit));
+}
+
+extern "C" int rg_gated_activation(const void* gu, void* out, int dtype, int T, int I, int kind, float limit,
+                                   void* stream) {
+    if (T <= 0 || I <= 0) return 0;
+    if (kind < 0 || kind > 2) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)T * I;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(gated_activation_kernel<bf16>, dim3(blocks), dim3(256), 0, s, 1, (const bf16*)gu, (bf16*)out, I,
+                         kind, limit, total);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(gated_activation_kernel<float>, dim3(blocks), dim3(256), 0, s, 1, (const float*)gu, (float*)out, I,
+                         kind, limit, total);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -2,8 +2,10 @@
 // size up to 256, any page size, 32-bit or bfloat16 storage, all arithmetic in
 // 32-bit.  It serves the true 32-bit path and every shape the fast kernels
 // refuse.  A query at absolute position p of request r attends the keys of r
-// at positions [max(0, p - window + 1), p], read from the paged cache through
-// r's block table (the step's own keys are written before it runs).
+// at positions [max(0, p - window + 1), p] and, with keep_first, also the first
+// keep_first positions of r whatever the window (kept tokens keep their own
+// positions), read from the paged cache through r's block table (the step's
+// own keys are written before it runs).
 //
 // Formulas: kv_head = head / (nh / nkv); s_j = scale * q.k_j; running max m,
 // p_j = exp(s_j - m), out = sum p_j v_j / sum p_j
@@ -21,7 +23,7 @@ template <typename A>
 __global__ void paged_attention_general_kernel(
         const A* __restrict__ q, int q_stride, A* __restrict__ out, const A* __restrict__ kv_cache,
         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ req_of_token,
-        const int* __restrict__ positions, int nh, int nkv, int d, int page_size, int window, float scale) {
+        const int* __restrict__ positions, int nh, int nkv, int d, int page_size, int window, float scale, int keep_first) {
     extern __shared__ float smem[];
     float* qs = smem;                    // [d]
     float* ps = qs + d;                  // [ATT_THREADS]
@@ -41,10 +43,14 @@ __global__ void paged_attention_general_kernel(
     float m = -INFINITY, l = 0.f;
     float acc0 = 0.f, acc1 = 0.f;        // output dims threadIdx.x and threadIdx.x + 128
     const size_t page_elems = (size_t)2 * nkv * page_size * d;
-    for (int base = lo; base <= pos; base += ATT_THREADS) {
-        const int j = base + threadIdx.x;
+    // the keys a query sees, numbered 0 .. n_sink + (pos - lo): the kept first tokens that the window has passed, then the window
+    const int n_sink = min(keep_first, lo);
+    const int n_seen = n_sink + pos - lo + 1;
+    for (int base = 0; base < n_seen; base += ATT_THREADS) {
+        const int e = base + threadIdx.x;
+        const int j = e < n_sink ? e : lo + (e - n_sink);
         float s = -INFINITY;
-        if (j <= pos) {
+        if (e < n_seen) {
             const int page = bt[j / page_size], off = j % page_size;
             const A* krow = kv_cache + (size_t)page * page_elems + ((size_t)kvh * page_size + off) * d;
             float dot = 0.f;
@@ -53,7 +59,7 @@ __global__ void paged_attention_general_kernel(
         }
         const float cmax = block_max(s, scratch);
         const float m_new = fmaxf(m, cmax);
-        const float p = (j <= pos) ? expf(s - m_new) : 0.f;
+        const float p = (e < n_seen) ? expf(s - m_new) : 0.f;
         const float alpha = expf(m - m_new);           // 0 when m = -inf
         const float csum = block_sum(p, scratch);
         l = l * alpha + csum;
@@ -62,9 +68,9 @@ __global__ void paged_attention_general_kernel(
         __syncthreads();
         acc0 *= alpha;
         acc1 *= alpha;
-        const int n = min(ATT_THREADS, pos - base + 1);
+        const int n = min(ATT_THREADS, n_seen - base);
         for (int k = 0; k < n; ++k) {
-            const int jj = base + k;
+            const int jj = base + k < n_sink ? base + k : lo + (base + k - n_sink);
             const int page = bt[jj / page_size], off = jj % page_size;
             const A* vrow = kv_cache + (size_t)page * page_elems
                             + ((size_t)(nkv + kvh) * page_size + off) * d;
@@ -83,19 +89,19 @@ __global__ void paged_attention_general_kernel(
 extern "C" int rg_paged_attention_general(
         const void* q, int q_stride, void* out, const void* kv_cache, int dtype,
         const int* block_table, int max_blocks, const int* req_of_token, const int* positions,
-        int T, int nh, int nkv, int d, int page_size, int window, float scale, void* stream) {
+        int T, int nh, int nkv, int d, int page_size, int window, float scale, int keep_first, void* stream) {
     if (T <= 0) return 0;
-    if (d > 2 * ATT_THREADS || d < 1 || nkv < 1 || nh < nkv || nh % nkv) return RG_ERR_UNSUPPORTED;
+    if (d > 2 * ATT_THREADS || d < 1 || nkv < 1 || nh < nkv || nh % nkv || keep_first < 0) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nh);
     const size_t smem = (size_t)(d + ATT_THREADS + 33) * sizeof(float);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(paged_attention_general_kernel<bf16>, grid, dim3(ATT_THREADS), smem, s, 1,
                          (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks,
-                         req_of_token, positions, nh, nkv, d, page_size, window, scale);
+                         req_of_token, positions, nh, nkv, d, page_size, window, scale, keep_first);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(paged_attention_general_kernel<float>, grid, dim3(ATT_THREADS), smem, s, 1,
                          (const float*)q, q_stride, (float*)out, (const float*)kv_cache, block_table, max_blocks,
-                         req_of_token, positions, nh, nkv, d, page_size, window, scale);
+                         req_of_token, positions, nh, nkv, d, page_size, window, scale, keep_first);
     return RG_ERR_UNSUPPORTED;
 }

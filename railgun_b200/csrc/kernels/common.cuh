@@ -71,6 +71,20 @@ __device__ __forceinline__ void rotary_cos_sin(double pos, double freq, float* c
     sincosf((float)r, s, c);
 }
 
+// The gated activations of feed-forwards, act(gate) * up in 32-bit.  kind 0: silu(g) u; 1: gelu (tanh form) of g, times u;
+// 2: the clamped form g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+#define RG_GATED_SILU 0
+#define RG_GATED_GELU_TANH 1
+#define RG_GATED_CLAMPED_SWISH 2
+__device__ __forceinline__ float gated_act(float g, float u, int kind, float limit) {
+    if (kind == RG_GATED_SILU) return g / (1.f + expf(-g)) * u;
+    if (kind == RG_GATED_GELU_TANH)
+        return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
 #define RG_LAUNCH_RESULT() ((int)cudaGetLastError())
 
 // Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel before it

@@ -22,7 +22,7 @@
 template <typename A>
 __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restrict__ router,
                                  const float* __restrict__ correction, int* __restrict__ ids,
-                                 float* __restrict__ weights, int T, int W, int N, int top) {
+                                 float* __restrict__ weights, int T, int W, int N, int top, int renormalize) {
     extern __shared__ float sm[];                 // per token of the block: N scores, N choice scores
     pdl_wait();
     pdl_trigger();
@@ -81,7 +81,7 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
         for (int n = lane; n < N; n += 32) { const float e = expf(s[n] - mx); s[n] = e; sum += e; }
         sum = warp_sum(sum);
         const float inv = 1.f / sum;
-        for (int n = lane; n < N; n += 32) { const float p = s[n] * inv; s[n] = p; c[n] = p + correction[n]; }
+        for (int n = lane; n < N; n += 32) { const float p = s[n] * inv; s[n] = p; c[n] = p + (correction ? correction[n] : 0.f); }
         __syncwarp();
         float chosen_sum = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -105,14 +105,14 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
             }
             __syncwarp();
         }
-        const float norm = 1.f / (chosen_sum + 1e-20f);
+        const float norm = renormalize ? 1.f / (chosen_sum + 1e-20f) : 1.f;
         for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= norm;
         __syncwarp();
     }
 }
 
 extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const float* correction, int* ids,
-                            float* weights, int T, int W, int N, int top, void* stream) {
+                            float* weights, int T, int W, int N, int top, int renormalize, void* stream) {
     if (T <= 0) return 0;
     if (top < 1 || top > N) return RG_ERR_UNSUPPORTED;
     const size_t smem = (size_t)ROUTE_TOKENS * 2 * N * sizeof(float);
@@ -122,10 +122,10 @@ extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const
     dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(warps * 32);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(moe_route_kernel<bf16>, grid, block, smem, s, 1, (const bf16*)x, router, correction, ids,
-                         weights, T, W, N, top);
+                         weights, T, W, N, top, renormalize);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(moe_route_kernel<float>, grid, block, smem, s, 1, (const float*)x, router, correction, ids,
-                         weights, T, W, N, top);
+                         weights, T, W, N, top, renormalize);
     return RG_ERR_UNSUPPORTED;
 }
 
@@ -206,7 +206,7 @@ extern "C" int rg_moe_align(const int* ids, int P, int E, int tile_rows, int* so
 template <typename A, bool GATED>
 __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(
         const A* __restrict__ a, int lda, const int* __restrict__ src, int src_div, const A* __restrict__ w,
-        A* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
+        A* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K, int act, float limit) {
     __shared__ float As[GG_BK][GG_BM + 1];
     __shared__ float Ws[GATED ? 2 : 1][GG_BK][GG_BN + 1];
     __shared__ int rowsrc[GG_BM];
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(
             const int n = n0 + tc + 16 * j;
             if (n >= N) continue;
             float v = acc[i][j];
-            if (GATED) v = v / (1.f + expf(-v)) * acc2[i][j];
+            if (GATED) v = gated_act(v, acc2[i][j], act, limit);
             out[(size_t)(first + r) * ldo + n] = from_f32<A>(v);
         }
     }
@@ -269,13 +269,13 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(
 
 extern "C" int rg_moe_grouped_gemm(const void* a, int lda, const int* src, int src_div, const void* w, void* out,
                                    int ldo, int dtype, const int* tiles, int max_tiles, int tile_rows, int N, int K,
-                                   int gated, void* stream) {
+                                   int gated, int act, float limit, void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
     if (tile_rows != GG_BM || K < 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(max_tiles, (N + GG_BN - 1) / GG_BN), block(256);
 #define RG_GG(A, G) return rg_launch(moe_grouped_gemm_kernel<A, G>, grid, block, 0, s, 1, (const A*)a, lda, src, \
-        src_div, (const A*)w, (A*)out, ldo, tiles, N, K)
+        src_div, (const A*)w, (A*)out, ldo, tiles, N, K, act, limit)
     if (dtype == RG_DTYPE_BF16 && gated) RG_GG(bf16, true);
     if (dtype == RG_DTYPE_BF16 && !gated) RG_GG(bf16, false);
     if (dtype == RG_DTYPE_F32 && gated) RG_GG(float, true);
@@ -369,7 +369,7 @@ extern "C" int rg_moe_gather_rows(const void* a, int lda, const int* src, int sr
 template <int BM, bool GATED>
 __global__ void __launch_bounds__(BM == 128 ? 256 : 128) moe_grouped_gemm_mma_kernel(
         const bf16* __restrict__ a, int lda, const int* __restrict__ src, int src_div, const bf16* __restrict__ w,
-        bf16* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
+        bf16* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K, int act, float limit) {
     using namespace rgmma;
     constexpr int THREADS = BM == 128 ? 256 : 128;
     constexpr int WARPS_M = BM == 128 ? 4 : 2;                     // x 2 warps along the columns
@@ -470,7 +470,7 @@ __global__ void __launch_bounds__(BM == 128 ? 256 : 128) moe_grouped_gemm_mma_ke
                     const int n = n0 + wn * 32 + ni * 8 + tq * 2 + c;
                     if (n >= N) continue;
                     float v = acc[0][mi][ni][half * 2 + c];
-                    if (GATED) v = v / (1.f + expf(-v)) * acc[NB - 1][mi][ni][half * 2 + c];
+                    if (GATED) v = gated_act(v, acc[NB - 1][mi][ni][half * 2 + c], act, limit);
                     orow[n] = __float2bfloat16_rn(v);
                 }
             }
@@ -485,7 +485,7 @@ template <typename KF> static int gm_allow_smem(KF kernel, size_t bytes) {
 // tile_rows: 32, the tile size `moe_align` was given.
 extern "C" int rg_moe_grouped_gemm_mma(const void* a, int lda, const int* src, int src_div, const void* w, void* out,
                                        int ldo, const int* tiles, int max_tiles, int tile_rows, int N, int K,
-                                       int gated, void* stream) {
+                                       int gated, int act, float limit, void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
     if (tile_rows != 32 || K < 8 || (K & 7) || (lda & 7) || src_div < 1) return RG_ERR_UNSUPPORTED;
     if (((uintptr_t)a | (uintptr_t)w) & 15) return RG_ERR_UNSUPPORTED;
@@ -495,7 +495,7 @@ extern "C" int rg_moe_grouped_gemm_mma(const void* a, int lda, const int* src, i
 #define RG_GM(BM, G) { const size_t smem = (size_t)GM_STAGES * (BM + (G ? 2 : 1) * GM_BN) * GM_STRIDE * 2; \
         e = gm_allow_smem(moe_grouped_gemm_mma_kernel<BM, G>, smem); if (e) return e; \
         return rg_launch(moe_grouped_gemm_mma_kernel<BM, G>, grid, dim3(BM == 128 ? 256 : 128), smem, s, 1, \
-                         (const bf16*)a, lda, src, src_div, (const bf16*)w, (bf16*)out, ldo, tiles, N, K); }
+                         (const bf16*)a, lda, src, src_div, (const bf16*)w, (bf16*)out, ldo, tiles, N, K, act, limit); }
     if (gated) RG_GM(32, true)
     RG_GM(32, false)
 #undef RG_GM

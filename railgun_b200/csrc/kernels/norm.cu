@@ -204,3 +204,89 @@ extern "C" int rg_residual_add(float* resid, const void* pending, int pending_dt
                          (size_t)n);
     return RG_ERR_UNSUPPORTED;
 }
+
+// RMSNorm in groups after up to two additions, with up to two weights (a block whose mixer and feed-forward
+// read the same stream, each through a norm of its own):
+//   r = residual[row] + (p1[row] + p2[row])                 32-bit, written back (not with `rows`)
+//   the row is cut into `groups` equal consecutive parts; each part is divided by its own sqrt(mean(part^2) + eps)
+//   out_k = w_k * that, k = 1, 2 (out2 may be absent)
+// The block's eight warps form teams of 8 / groups warps (at least one), a team per group at a time; a team adds
+// its squares in a fixed order, so a row's result does not depend on what else is in the step.
+__device__ __forceinline__ float load_any(const void* p, int dtype, size_t i) {
+    return dtype == RG_DTYPE_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i])
+                                  : reinterpret_cast<const float*>(p)[i];
+}
+
+template <typename O>
+__global__ void __launch_bounds__(256) add_group_rmsnorm_kernel(
+        float* __restrict__ resid, const void* __restrict__ p1, int p1_dtype, const void* __restrict__ p2, int p2_dtype,
+        const float* __restrict__ w1, const float* __restrict__ w2, float eps, O* __restrict__ out1,
+        O* __restrict__ out2, const int* __restrict__ rows, int H, int groups, int wpt) {
+    __shared__ float scratch[8];
+    pdl_wait();
+    pdl_trigger();
+    const int orow = blockIdx.x;
+    const int srow = rows ? rows[orow] : orow;
+    float* r = resid + (size_t)srow * H;
+    const size_t pbase = (size_t)srow * H;
+    const bool write_back = rows == nullptr && (p1 != nullptr || p2 != nullptr);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nteams = 8 / wpt, team = warp / wpt, in_team = (warp - team * wpt) * 32 + lane, team_threads = wpt * 32;
+    const int gs = H / groups;
+    for (int g0 = 0; g0 < groups; g0 += nteams) {
+        const int g = g0 + team;
+        const bool active = g < groups;
+        const int lo = g * gs;
+        float ss = 0.f;
+        if (active) {
+            for (int i = lo + in_team; i < lo + gs; i += team_threads) {
+                float v = r[i];
+                if (p1 || p2) {
+                    float add = p1 ? load_any(p1, p1_dtype, pbase + i) : 0.f;
+                    if (p2) add += load_any(p2, p2_dtype, pbase + i);
+                    v += add;
+                    if (write_back) r[i] = v;
+                }
+                ss += v * v;
+            }
+        }
+        ss = warp_sum(ss);
+        if (wpt > 1) {
+            if (lane == 0) scratch[warp] = ss;
+            __syncthreads();
+            ss = 0.f;
+            for (int k = 0; k < wpt; ++k) ss += scratch[team * wpt + k];
+            __syncthreads();
+        }
+        if (!active) continue;
+        const float inv = rsqrtf(ss / (float)gs + eps);
+        for (int i = lo + in_team; i < lo + gs; i += team_threads) {
+            float v = r[i];
+            if (!write_back && (p1 || p2)) {
+                float add = p1 ? load_any(p1, p1_dtype, pbase + i) : 0.f;
+                if (p2) add += load_any(p2, p2_dtype, pbase + i);
+                v += add;
+            }
+            v *= inv;
+            out1[(size_t)orow * H + i] = from_f32<O>(v * w1[i]);
+            if (out2) out2[(size_t)orow * H + i] = from_f32<O>(v * w2[i]);
+        }
+    }
+}
+
+extern "C" int rg_add_group_rmsnorm(float* resid, const void* p1, int p1_dtype, const void* p2, int p2_dtype,
+                                    const float* w1, const float* w2, float eps, void* out1, void* out2, int out_dtype,
+                                    const int* rows, int n_out_rows, int H, int groups, void* stream) {
+    if (n_out_rows <= 0) return 0;
+    if (groups < 1 || H % groups || (out2 && !w2)) return RG_ERR_UNSUPPORTED;
+    int wpt = 8;
+    while (wpt > 1 && wpt * groups > 8) wpt >>= 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == RG_DTYPE_BF16)
+        return rg_launch(add_group_rmsnorm_kernel<bf16>, dim3(n_out_rows), dim3(256), 0, s, 1, resid, p1, p1_dtype, p2,
+                         p2_dtype, w1, w2, eps, (bf16*)out1, (bf16*)out2, rows, H, groups, wpt);
+    if (out_dtype == RG_DTYPE_F32)
+        return rg_launch(add_group_rmsnorm_kernel<float>, dim3(n_out_rows), dim3(256), 0, s, 1, resid, p1, p1_dtype, p2,
+                         p2_dtype, w1, w2, eps, (float*)out1, (float*)out2, rows, H, groups, wpt);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -108,14 +108,14 @@ def _fn(lib_name: str, fn_name: str):
     return fn
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-    """residual [T, H] float32 = table[ids]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """residual [T, H] float32 = table[ids] * scale."""
     _check(ids, "ids", torch.int32)
     _check(table, "table")
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     _ok(_fn("embedding", "rg_embedding")(_ptr(ids), _ptr(table), c_int(_dtype_code(table)), _ptr(out),
-                                         c_int(T), c_int(H), c_int(V), _stream()), "embedding")
+                                         c_int(T), c_int(H), c_int(V), c_float(scale), _stream()), "embedding")
     return out
 
 
@@ -143,6 +143,62 @@ def add_rmsnorm(resid: torch.Tensor, pending, weight: torch.Tensor, eps: float, 
         "add_rmsnorm")
     return out
 
+
+
+class PendingSum:
+    """The outputs of several parts that read the same stream (a mixer and a
+    feed-forward side by side), still to be added to it: first to one another,
+    then to the residual, in 32-bit, inside the next norm's kernel."""
+
+    def __init__(self, parts):
+        self.parts = [p for p in parts if p is not None]
+        if not 1 <= len(self.parts) <= 2:
+            raise KernelError(f"a pending sum holds one or two outputs, not {len(self.parts)}")
+
+    def materialize(self) -> torch.Tensor:
+        """The sum as one 32-bit tensor, for a norm that takes tensors only."""
+        out = self.parts[0].to(torch.float32, copy=True)
+        for p in self.parts[1:]:
+            out += p
+        return out
+
+
+def add_group_rmsnorm(resid: torch.Tensor, pending, weights, groups: int, eps: float, out_dtype,
+                      rows: torch.Tensor | None = None):
+    """resid += (the sum of ``pending``: None, a tensor, or a ``PendingSum`` of
+    up to two) in place, in 32-bit; then RMSNorm of resid in ``groups`` equal
+    consecutive parts, each divided by its own root mean square, once per
+    weight vector in ``weights`` (one or two: branches that read the same
+    stream through norms of their own).  Returns one output per weight.  With
+    ``rows`` (int32 indices) only those rows are normed and resid is untouched."""
+    _check(resid, "resid", torch.float32)
+    T, H = resid.shape
+    if groups < 1 or H % groups:
+        raise KernelError(f"rows of {H} do not split into {groups} equal groups")
+    if not 1 <= len(weights) <= 2:
+        raise KernelError("add_group_rmsnorm: one or two weight vectors")
+    for w in weights:
+        _check(w, "weight", torch.float32)
+        if w.numel() != H:
+            raise KernelError(f"norm weight has {w.numel()} elements, rows have {H}")
+    parts = pending.parts if isinstance(pending, PendingSum) else ([pending] if pending is not None else [])
+    for p in parts:
+        _check(p, "pending")
+        if p.shape != resid.shape:
+            raise KernelError(f"pending {tuple(p.shape)} vs residual {tuple(resid.shape)}")
+    n_out = T
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    outs = [torch.empty((n_out, H), dtype=out_dtype, device=resid.device) for _ in weights]
+    p1 = parts[0] if parts else None
+    p2 = parts[1] if len(parts) > 1 else None
+    _ok(_fn("norm", "rg_add_group_rmsnorm")(
+        _ptr(resid), _ptr(p1), c_int(_dtype_code(p1) if p1 is not None else 0), _ptr(p2),
+        c_int(_dtype_code(p2) if p2 is not None else 0), _ptr(weights[0]), _ptr(weights[1] if len(weights) > 1 else None),
+        c_float(eps), _ptr(outs[0]), _ptr(outs[1] if len(outs) > 1 else None), c_int(_dtype_code(outs[0])), _ptr(rows),
+        c_int(n_out), c_int(H), c_int(groups), _stream()), "add_group_rmsnorm")
+    return outs
 
 
 class PendingNormed:
@@ -392,22 +448,25 @@ def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
 MOE_TILE_ROWS = 32
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int):
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction, top: int, renormalize: bool = True):
     """Router of a mixture of experts: softmax of the 32-bit logits ``router`` x
-    over all N outputs; the ``top`` outputs with the largest score + correction;
-    weights = their scores over their sum.  Returns (ids int32 [T, top],
-    weights float32 [T, top])."""
+    over all N outputs; the ``top`` outputs with the largest score + correction
+    (``correction`` None: the largest scores); weights = their scores over
+    their sum, or with ``renormalize`` False the scores themselves.  Returns
+    (ids int32 [T, top], weights float32 [T, top])."""
     _check(x, "x")
     _check(router, "router", torch.float32)
-    _check(correction, "correction", torch.float32)
+    if correction is not None:
+        _check(correction, "correction", torch.float32)
     T, W = x.shape
     N = router.shape[0]
-    if router.shape[1] != W or correction.numel() != N:
-        raise KernelError(f"router {tuple(router.shape)}, correction {correction.numel()} vs rows of {W}")
+    if router.shape[1] != W or (correction is not None and correction.numel() != N):
+        raise KernelError(f"router {tuple(router.shape)} or its correction do not match rows of {W}")
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
     _ok(_fn("moe", "rg_moe_route")(_ptr(x), c_int(_dtype_code(x)), _ptr(router), _ptr(correction), _ptr(ids),
-                                   _ptr(weights), c_int(T), c_int(W), c_int(N), c_int(top), _stream()), "moe_route")
+                                   _ptr(weights), c_int(T), c_int(W), c_int(N), c_int(top), c_int(1 if renormalize else 0),
+                                   _stream()), "moe_route")
     return ids, weights
 
 
@@ -427,8 +486,27 @@ def moe_align(ids: torch.Tensor, num_experts: int, tile_rows: int = MOE_TILE_ROW
     return sorted_pair, pair_pos, tiles
 
 
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def gated_activation(gate_up: torch.Tensor, kind: str = "silu", limit: float = 0.0) -> torch.Tensor:
+    """[T, 2I] = gate | up -> [T, I] = act(gate) * up in 32-bit: "silu", "gelu_tanh", or "clamped_swish":
+    g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)."""
+    _check(gate_up, "gate_up")
+    if kind not in GATED_ACTIVATIONS:
+        raise KernelError(f"unknown gated activation {kind!r}; known: {sorted(GATED_ACTIVATIONS)}")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gated_activation: last dimension must be even")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _ok(_fn("activation", "rg_gated_activation")(_ptr(gate_up), _ptr(out), c_int(_dtype_code(gate_up)), c_int(T),
+                                                 c_int(two_i // 2), c_int(GATED_ACTIVATIONS[kind]), c_float(limit),
+                                                 _stream()), "gated_activation")
+    return out
+
+
 def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles: torch.Tensor, places: int,
-                     gated: bool, tile_rows: int = MOE_TILE_ROWS) -> torch.Tensor:
+                     gated: bool, tile_rows: int = MOE_TILE_ROWS, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """out[pos] = W_e a_row(pos) for every place of the tile list, e the tile's
     expert; ``w`` [E, N, K] (``gated``: [E, 2 N, K] = gate rows then up rows and
     out = silu(gate) * up).  Row ``pos`` of the input is ``a[src[pos] // src_div]``
@@ -467,18 +545,22 @@ def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles:
         _ok(_fn("gemm_tcgen05", "rg_tc_gemm_grouped")(
             _ptr(a), c_int(a.stride(0)), c_int(places), _ptr(w), c_int(E), c_int(rows_w), c_int(K), _ptr(wide),
             c_int(rows_w), _ptr(tiles), c_int(tiles.shape[0]), _ptr(err), _stream()), "tc_gemm_grouped")
-        return silu_mul(wide) if gated else wide
+        if not gated:
+            return wide
+        return silu_mul(wide) if act == "silu" else gated_activation(wide, act, limit)
+    if act not in GATED_ACTIVATIONS:
+        raise KernelError(f"unknown gated activation {act!r}; known: {sorted(GATED_ACTIVATIONS)}")
     out = torch.empty((places, N), dtype=a.dtype, device=a.device)
     if moe_grouped_gemm_tc_ok(a.dtype, K, a.stride(0)):
         _ok(_fn("moe", "rg_moe_grouped_gemm_mma")(
             _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), _ptr(tiles),
-            c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0), _stream()),
-            "moe_grouped_gemm_mma")
+            c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0),
+            c_int(GATED_ACTIVATIONS[act]), c_float(limit), _stream()), "moe_grouped_gemm_mma")
         return out
     _ok(_fn("moe", "rg_moe_grouped_gemm")(
         _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), c_int(_dtype_code(a)),
-        _ptr(tiles), c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0), _stream()),
-        "moe_grouped_gemm")
+        _ptr(tiles), c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0),
+        c_int(GATED_ACTIVATIONS[act]), c_float(limit), _stream()), "moe_grouped_gemm")
     return out
 
 
@@ -737,6 +819,181 @@ def recurrent_scan(proj: torch.Tensor, y_off: int, x_off: int, yb, xb, u: torch.
         _ptr(batch.start_pos), _ptr(batch.state_slots), _ptr(out), c_int(out.stride(0)), c_float(out_scale), c_int(T),
         c_int(R), c_int(C), c_int(K), c_int(bs), _ptr(ab), c_int(batch.max_query_len), _stream()), "recurrent_scan")
     return out
+
+
+# ---- short convolutions with state, matrix-state mixers (retention, delta rule), attention's per-token work -------
+
+def causal_conv(x: torch.Tensor, x_off: int, taps: torch.Tensor, state, batch, out_dtype, residual: bool = False,
+                silu: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """[T, C]: per channel the causal convolution of x[:, x_off:x_off + C] with ``taps`` [C, K] (last column: the
+    current token's) along each request's tokens, continued from the K - 1 inputs in the request's state slot
+    (``state`` [slots, K - 1, C] float32; None when K = 1) unless the request starts at position 0.  ``silu``:
+    the activation on the convolution; ``residual``: x is added.  32-bit arithmetic, one rounding into
+    ``out_dtype``.  The state is not changed (``conv_state_update`` does that, afterwards)."""
+    _check_rows(x, "x")
+    _check(taps, "taps", torch.float32)
+    C, K = taps.shape
+    T = x.shape[0]
+    if x.shape[1] < x_off + C:
+        raise KernelError(f"causal_conv: {C} channels from column {x_off} of rows of {x.shape[1]}")
+    if K > 1:
+        _check(state, "state", torch.float32)
+        if tuple(state.shape[1:]) != (K - 1, C):
+            raise KernelError(f"causal_conv: state {tuple(state.shape)} is not [slots, {K - 1}, {C}]")
+    if out is None:
+        out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+    _check_out_view(out, T, C, out_dtype, "causal_conv")
+    _ok(_fn("state_mixers", "rg_causal_conv")(
+        _ptr(x), c_int(_dtype_code(x)), c_int(x.stride(0)), c_int(x_off), _ptr(taps), _ptr(state if K > 1 else None),
+        _ptr(batch.cu_seqlens), _ptr(batch.req_of_token), _ptr(batch.start_pos), _ptr(batch.state_slots), _ptr(out),
+        c_int(_dtype_code(out)), c_int(out.stride(0)), c_int(T), c_int(C), c_int(K), c_int(1 if residual else 0),
+        c_int(1 if silu else 0), _stream()), "causal_conv")
+    return out
+
+
+def conv_state_update(x: torch.Tensor, x_off: int, state: torch.Tensor, batch) -> None:
+    """Leave the last K - 1 inputs x[:, x_off:x_off + C] of every request of the step in its slot of ``state``
+    [slots, K - 1, C] (older ones move up when the step brought fewer than K - 1 tokens)."""
+    _check_rows(x, "x")
+    _check(state, "state", torch.float32)
+    K1, C = state.shape[1:]
+    if K1 < 1:
+        return
+    _ok(_fn("state_mixers", "rg_conv_state_update")(
+        _ptr(x), c_int(_dtype_code(x)), c_int(x.stride(0)), c_int(x_off), _ptr(state), _ptr(batch.cu_seqlens),
+        _ptr(batch.start_pos), _ptr(batch.state_slots), c_int(batch.num_requests), c_int(C), c_int(K1 + 1), _stream()),
+        "conv_state_update")
+
+
+def retention_prepare(proj: torch.Tensor, q_off: int, k_off: int, freq: torch.Tensor, rot_dims: int,
+                      positions: torch.Tensor, H: int, d: int, k_scale: float):
+    """q, k [T, H, d] float32 from the columns of ``proj`` at ``q_off`` and ``k_off``: the first ``rot_dims`` numbers
+    of every head rotated in pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64), k times ``k_scale``."""
+    _check_rows(proj, "proj")
+    _check(freq, "freq", torch.float64)
+    _check(positions, "positions", torch.int32)
+    T = proj.shape[0]
+    if proj.shape[1] < max(q_off, k_off) + H * d or freq.numel() < rot_dims // 2:
+        raise KernelError("retention_prepare: sizes do not match")
+    q = torch.empty((T, H, d), dtype=torch.float32, device=proj.device)
+    k = torch.empty((T, H, d), dtype=torch.float32, device=proj.device)
+    _ok(_fn("state_mixers", "rg_retention_prepare")(
+        _ptr(proj), c_int(_dtype_code(proj)), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), _ptr(freq),
+        c_int(rot_dims), _ptr(positions), _ptr(q), _ptr(k), c_int(T), c_int(H), c_int(d), c_float(k_scale), _stream()),
+        "retention_prepare")
+    return q, k
+
+
+def delta_prepare(qkv: torch.Tensor, G: int, d: int, q_scale: float, unit_eps: float, ab: torch.Tensor, b_off: int,
+                  a_off: int, A_log: torch.Tensor, dt_bias: torch.Tensor, H: int):
+    """In place on ``qkv`` [T, >= 2 G d] float32: the G query heads (from column 0) and the G key heads (from
+    column G d) become unit vectors, x / sqrt(sum(x^2) + ``unit_eps``), the queries times ``q_scale``.  Returns
+    beta = sigmoid(ab[:, b_off:b_off + H]) and g = exp(-exp(A_log) softplus(ab[:, a_off:a_off + H] + dt_bias)),
+    both [T, H] float32."""
+    _check_rows(qkv, "qkv", torch.float32)
+    _check_rows(ab, "ab")
+    _check(A_log, "A_log", torch.float32)
+    _check(dt_bias, "dt_bias", torch.float32)
+    T = qkv.shape[0]
+    if qkv.shape[1] < 2 * G * d or ab.shape[0] != T or ab.shape[1] < max(a_off, b_off) + H or A_log.numel() != H \
+            or dt_bias.numel() != H:
+        raise KernelError("delta_prepare: sizes do not match")
+    beta = torch.empty((T, H), dtype=torch.float32, device=qkv.device)
+    g = torch.empty((T, H), dtype=torch.float32, device=qkv.device)
+    _ok(_fn("state_mixers", "rg_delta_prepare")(
+        _ptr(qkv), c_int(qkv.stride(0)), c_int(G), c_int(d), c_float(q_scale), c_float(unit_eps), _ptr(ab),
+        c_int(_dtype_code(ab)), c_int(ab.stride(0)), c_int(b_off), c_int(a_off), _ptr(A_log), _ptr(dt_bias), _ptr(beta),
+        _ptr(g), c_int(T), c_int(H), _stream()), "delta_prepare")
+    return beta, g
+
+
+def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, batch, H: int, d: int, dv: int,
+               decay: torch.Tensor | None = None, g: torch.Tensor | None = None,
+               beta: torch.Tensor | None = None) -> torch.Tensor:
+    """A matrix S [d, dv] per head carried along each request's tokens, 32-bit, from the request's slot of ``state``
+    [slots, H, d, dv] (zeros at position 0) and left there.  With ``decay`` [H]: S <- decay_h S + k v^T; with ``g``
+    and ``beta`` [T, H]: S <- g S, u = beta (v - S^T k), S <- S + k u^T.  Either way o = S^T q after the update.
+    ``q``, ``k``: float32 [T, Hqk * d] views (head h reads head h / (H / Hqk)); ``v``: [T, H * dv] view, float32 or
+    bfloat16.
+    Returns o [T, H, dv] float32."""
+    for t, name in ((q, "q"), (k, "k")):
+        _check_rows(t, name, torch.float32)
+    _check_rows(v, "v")
+    _check(state, "state", torch.float32)
+    T = q.shape[0]
+    Hqk = q.shape[1] // d
+    if q.shape[1] != Hqk * d or k.shape != q.shape or v.shape != (T, H * dv) or Hqk < 1 or H % Hqk \
+            or tuple(state.shape[1:]) != (H, d, dv):
+        raise KernelError(f"state_scan: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, state "
+                          f"{tuple(state.shape)} do not match {H} heads of {d} x {dv}")
+    for t, name, n in ((decay, "decay", H), (g, "g", T * H), (beta, "beta", T * H)):
+        if t is not None:
+            _check(t, name, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"state_scan: {name} has {t.numel()} elements, expected {n}")
+    if (decay is None) == (g is None) or (beta is not None and g is None):
+        raise KernelError("state_scan: a fixed decay per head, or g and beta per token")
+    o = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
+    _ok(_fn("state_mixers", "rg_state_scan")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), _ptr(v), c_int(_dtype_code(v)), c_int(v.stride(0)),
+        _ptr(decay), _ptr(g),
+        _ptr(beta), _ptr(state), _ptr(batch.cu_seqlens), _ptr(batch.start_pos), _ptr(batch.state_slots), _ptr(o),
+        c_int(batch.num_requests), c_int(H), c_int(Hqk), c_int(d), c_int(dv), _stream()), "state_scan")
+    return o
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight, eps: float, out_dtype) -> torch.Tensor:
+    """[T, H dv] in ``out_dtype``: every head of ``o`` [T, H, dv] (float32) divided by its root mean square (``eps``
+    inside the root), times ``weight`` [dv] (None: no weight), times silu(``gate``) ([T, H dv] view)."""
+    _check(o, "o", torch.float32)
+    _check_rows(gate, "gate")
+    T, H, dv = o.shape
+    if gate.shape != (T, H * dv):
+        raise KernelError(f"head_norm_gate: gate {tuple(gate.shape)} vs o {tuple(o.shape)}")
+    if weight is not None:
+        _check(weight, "weight", torch.float32)
+        if weight.numel() != dv:
+            raise KernelError(f"head_norm_gate: weight has {weight.numel()} elements, heads have {dv}")
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    _ok(_fn("state_mixers", "rg_head_norm_gate")(
+        _ptr(o), _ptr(gate), c_int(_dtype_code(gate)), c_int(gate.stride(0)), c_int(0), _ptr(weight), c_float(eps),
+        _ptr(out), c_int(_dtype_code(out)), c_int(T), c_int(H), c_int(dv), _stream()), "head_norm_gate")
+    return out
+
+
+def attention_prepare(qkv: torch.Tensor, kv_cache, q_norm, k_norm, eps: float, freq: torch.Tensor, rot_dims: int,
+                      interleaved: bool, positions: torch.Tensor, slots, factor, H: int, G: int, d: int, dv: int,
+                      D: int) -> torch.Tensor:
+    """Per token of ``qkv`` [T, H d + G d + G dv]: q and k heads RMS-normed over d (``q_norm`` / ``k_norm`` [d]
+    float32, None: no norm), their first ``rot_dims`` numbers rotated in pairs (2i, 2i + 1) (``interleaved``) or
+    (i, i + rot_dims / 2) by position * ``freq[i]`` (float64), q head h times ``factor[h]`` (float32 [H] or None).
+    Returns q [T, H, D]; k and v go to place ``slots[t]`` of ``kv_cache`` [pages, 2, G, page, D] (negative slot
+    or None: no write).  D >= max(d, dv): the rest of every row is zeros."""
+    _check_rows(qkv, "qkv")
+    _check(freq, "freq", torch.float64)
+    _check(positions, "positions", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (H + G) * d + G * dv or positions.numel() != T or freq.numel() < rot_dims // 2:
+        raise KernelError(f"attention_prepare: qkv {tuple(qkv.shape)} does not match {H} + {G} heads of {d}, values of {dv}")
+    for w, name, n in ((q_norm, "q_norm", d), (k_norm, "k_norm", d), (factor, "factor", H)):
+        if w is not None:
+            _check(w, name, torch.float32)
+            if w.numel() != n:
+                raise KernelError(f"attention_prepare: {name} has {w.numel()} elements, expected {n}")
+    page_size = 1
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        _check(kv_cache, "kv_cache", qkv.dtype)
+        page_size = kv_cache.shape[3]
+        if tuple(kv_cache.shape[1:]) != (2, G, page_size, D):
+            raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match {G} heads of {D}")
+    q = torch.empty((T, H, D), dtype=qkv.dtype, device=qkv.device)
+    _ok(_fn("attention_prepare", "rg_attention_prepare")(
+        _ptr(qkv), c_int(_dtype_code(qkv)), c_int(qkv.stride(0)), _ptr(q), _ptr(kv_cache if slots is not None else None),
+        _ptr(q_norm), _ptr(k_norm), c_float(eps), _ptr(freq), c_int(rot_dims), c_int(1 if interleaved else 0),
+        _ptr(positions), _ptr(slots), _ptr(factor), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv), c_int(D),
+        c_int(page_size), _stream()), "attention_prepare")
+    return q
 
 
 ACTIVATIONS = {"relu2": 0, "relu": 1, "gelu_tanh": 2, "silu": 3}
@@ -1014,9 +1271,11 @@ def skinny_rope_ok(x, weight: torch.Tensor, d: int) -> bool:
 
 def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tensor, block_table: torch.Tensor,
                             req_of_token: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int, d: int,
-                            window: int, scale: float) -> torch.Tensor:
+                            window: int, scale: float, keep_first: int = 0) -> torch.Tensor:
     """The general attention kernel: out [T, nh*d].  ``q`` may be a view whose
-    rows are ``q_stride`` elements apart (the q part of a fused qkv buffer)."""
+    rows are ``q_stride`` elements apart (the q part of a fused qkv buffer).
+    ``keep_first``: with a window, the first positions of a request that every
+    later query still sees."""
     if not q.is_cuda:
         raise KernelError("q must be a CUDA tensor (there is no CPU path)")
     _check(kv_cache, "kv_cache", q.dtype)
@@ -1033,7 +1292,8 @@ def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tens
     _ok(_fn("attention_general", "rg_paged_attention_general")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), c_int(_dtype_code(q)), _ptr(block_table),
         c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), c_int(T), c_int(nh), c_int(nkv),
-        c_int(d), c_int(page_size), c_int(window or 0), c_float(scale), _stream()), "paged_attention_general")
+        c_int(d), c_int(page_size), c_int(window or 0), c_float(scale), c_int(keep_first if window else 0), _stream()),
+        "paged_attention_general")
     return out
 
 
@@ -1465,8 +1725,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k, top_p, seed: 
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tensor:
-    """y = x W^T, W stored [out, in].  Up to 64 bfloat16 rows go through the
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x W^T (+ ``bias``, added inside the library product), W stored [out, in].  Up to 64 bfloat16 rows go through the
     weight-streaming kernel of this package; everything else through the
     library matrix product (cuBLAS), as in the reference, whose projections
     are library GEMMs (crates/vllm-models/src/llama/attention.rs:94-96,133).
@@ -1482,6 +1742,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
         raise KernelError("linear: CUDA tensors only (there is no CPU path)")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("linear: TF32 is enabled; the 32-bit path must be true 32-bit")
+    if bias is not None:
+        if out_dtype is not None and out_dtype != x.dtype:
+            raise KernelError("linear: a product with a bias comes out in its input's type")
+        return torch.addmm(bias, x, weight.t())
     if x.shape[0] <= SKINNY_AUTO_ROWS and skinny_gemm_ok(x, weight):
         return skinny_gemm(x, weight, out_dtype)             # small decode batches: stream the weights once
     if out_dtype is not None and out_dtype != x.dtype:

@@ -17,6 +17,7 @@ from .. import ops
 from ..cache.manager import PagedKVNeed
 from ..weights.loader import TensorSpec
 from .base import Mixer
+from .latent_attention import rotary_frequencies
 from .registry import register_mixer, POSITION_ENCODINGS
 
 
@@ -136,3 +137,133 @@ class PagedAttention(Mixer):
 
 
 register_mixer("paged_attention", PagedAttention)
+
+
+class NormedAttention(Mixer):
+    """Grouped-query softmax attention with the options that recent designs add to it, each a parameter:
+    biases on the four projections, an RMS norm on every q and k head (one weight vector for all q heads, one
+    for all k heads) before the rotation, rotation of the first ``rot_dims`` numbers of a head in either
+    layout, a learned number per head on the scores (``head_temp``), values of another size than keys, and a
+    sliding window that keeps the request's first ``keep_first`` tokens visible (at their true positions).
+
+    Keys, queries and values are padded with zeros to one size D (a multiple of 16 that holds both), so the
+    key/value pages and the attention kernels are the ordinary ones; the output product's matrix gets zero
+    columns to match.  The score's scale and the head's number are multiplied into q, in 32-bit, before its
+    one rounding.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_dim``, ``scale`` (None:
+    head_dim^-1/2), ``rot_dims``, ``rot_base``, ``rot_layout`` ("interleaved": pairs (2i, 2i + 1), or "half":
+    pairs (i, i + rot_dims/2)), ``eps`` (of the q and k norms), ``window`` (0: none), ``keep_first``,
+    ``bias``, ``qk_norm``, ``head_temp`` (booleans, default true), ``base`` (what the tensor names start with
+    after the prefix, default "mix."; the tensors are q, k, v, o, their biases <name>.b, q.norm, k.norm, temp)."""
+
+    @classmethod
+    def _base(cls, p, prefix):
+        return prefix + (p.get("base") if p.get("base") is not None else "mix.")
+
+    @classmethod
+    def _padded(cls, p) -> int:
+        return -(-max(int(p["head_dim"]), int(p["v_dim"])) // 16) * 16
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        W, H, G, d, dv = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"], p["v_dim"]
+        b = cls._base(p, prefix)
+        out = {b + "q": TensorSpec((H * d, W)), b + "k": TensorSpec((G * d, W)), b + "v": TensorSpec((G * dv, W)),
+               b + "o": TensorSpec((W, H * dv))}
+        if p.get("bias", True):
+            out.update({b + "q.b": TensorSpec((H * d,)), b + "k.b": TensorSpec((G * d,)),
+                        b + "v.b": TensorSpec((G * dv,)), b + "o.b": TensorSpec((W,))})
+        if p.get("qk_norm", True):
+            out[b + "q.norm"] = TensorSpec((d,), init="norm")
+            out[b + "k.norm"] = TensorSpec((d,), init="norm")
+        if p.get("head_temp", True):
+            out[b + "temp"] = TensorSpec((H,), init="norm")
+        return out
+
+    @classmethod
+    def cache_need(cls, p):
+        window = int(p.get("window") or 0)
+        return PagedKVNeed(int(p["num_kv_heads"]), cls._padded(p), window,
+                           keep_first=int(p.get("keep_first") or 0) if window else 0)
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        self.H, self.G, self.d, self.dv = (int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"]),
+                                           int(p["v_dim"]))
+        self.D = self._padded(p)
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads cannot share {self.G} key/value heads")
+        if self.D > 256:
+            raise ValueError(f"head size {self.D} is above the attention kernels' limit of 256")
+        self.rot_dims = int(p.get("rot_dims") or 0)
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.d:
+            raise ValueError(f"{self.rot_dims} rotated numbers do not fit a head of {self.d}")
+        layout = p.get("rot_layout") or "interleaved"
+        if layout not in ("interleaved", "half"):
+            raise ValueError(f"rotation layout {layout!r} is not known; known: ['half', 'interleaved']")
+        self.interleaved = layout == "interleaved"
+        self.window = int(p.get("window") or 0)
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.eps = float(p.get("eps") or 0.0)
+        scale = float(p["scale"]) if p.get("scale") is not None else float(self.d) ** -0.5
+        b = self._base(p, prefix)
+        self.w_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in ("q", "k", "v")], dim=0).contiguous()
+        self.b_qkv = self.b_o = None
+        if p.get("bias", True):
+            self.b_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in ("q.b", "k.b", "v.b")], dim=0).contiguous()
+            self.b_o = tensors.get(b + "o.b", env.dtype).contiguous()
+        tensors.drop(b + "q", b + "k", b + "v", b + "q.b", b + "k.b", b + "v.b")
+        w_o = tensors.get(b + "o", env.dtype)
+        if self.D != self.dv:
+            # zero columns where the attention's output rows carry padding
+            padded = torch.zeros((w_o.shape[0], self.H, self.D), dtype=w_o.dtype, device=w_o.device)
+            padded[:, :, :self.dv] = w_o.view(w_o.shape[0], self.H, self.dv)
+            w_o = padded.view(w_o.shape[0], self.H * self.D)
+            tensors.drop(b + "o")
+        self.w_o = w_o.contiguous()
+        norm = p.get("qk_norm", True)
+        self.q_norm = tensors.get(b + "q.norm", torch.float32).contiguous() if norm else None
+        self.k_norm = tensors.get(b + "k.norm", torch.float32).contiguous() if norm else None
+        # what every q head is multiplied by: the score's scale times the head's own number
+        self.factor = torch.full((self.H,), scale, dtype=torch.float32, device=env.device)
+        if p.get("head_temp", True):
+            self.factor = (self.factor * tensors.get(b + "temp", torch.float32)).contiguous()
+        base = float(p.get("rot_base") or 10000.0)
+        self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
+                                        lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
+
+    def forward(self, x, batch, cache, writes=True):
+        H, G, d, dv, D = self.H, self.G, self.d, self.dv, self.D
+        qkv = ops.linear(x, self.w_qkv, bias=self.b_qkv)
+        slots = batch.slot_mapping[cache.group] if writes else None
+        q = ops.attention_prepare(qkv, cache.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
+                                  self.interleaved, batch.positions, slots, self.factor, H, G, d, dv, D)
+        out = self.attend(q.view(-1, H * D), batch, cache)
+        return ops.linear(out, self.w_o, bias=self.b_o)
+
+    def attend(self, q, batch, cache):
+        """bfloat16 runs on the tensor cores (requests with several tokens through the flash-style kernel, single
+        tokens through the split kernel); the 32-bit path runs the general kernel."""
+        H, G, D = self.H, self.G, self.D
+        table = batch.block_table[cache.group]
+        if q.dtype != torch.bfloat16 or self.keep_first:
+            return ops.paged_attention_general(q, q.shape[1], cache.kv, table, batch.req_of_token, batch.positions,
+                                               H, G, D, self.window, 1.0, self.keep_first)
+        out = torch.empty((q.shape[0], H * D), dtype=q.dtype, device=q.device)
+        kv_tiles = G * (-(-(H // G) // 8))
+        reach = batch.max_context_len
+        if self.window:
+            reach = min(reach, self.window + self.keep_first)
+        if batch.num_prefill_tiles:
+            ops.prefill_attention(q, q.shape[1], out, cache.kv, table, batch.prefill_tiles, batch.positions,
+                                  H, G, D, self.window, 1.0)
+        n = batch.num_tokens if batch.decode_only else batch.num_decode_rows
+        if n:
+            ops.decode_attention(q, q.shape[1], out, cache.kv, table, None if batch.decode_only else batch.decode_rows,
+                                 n, batch.req_of_token, batch.positions, H, G, D, self.window, 1.0,
+                                 ops.decode_splits(n, kv_tiles, reach))
+        return out
+
+
+register_mixer("gqa_attention", NormedAttention)

@@ -77,6 +77,8 @@ def normed_input(norm, part, stream, rows=None):
         pending = pending.materialize()
     if isinstance(pending, ops.PendingNormed) and not getattr(norm, "fuses_post_norm", False):
         pending = pending.materialize()
+    if isinstance(pending, ops.PendingSum) and not getattr(norm, "fuses_pending_sum", False):
+        pending = pending.materialize()
     h = norm.add_norm(stream.resid, pending) if rows is None else norm.add_norm(stream.resid, pending, rows=rows)
     if isinstance(h, ops.NormedRows) and not getattr(part, "takes_normed_rows", False):
         h = h.materialize()

@@ -21,6 +21,13 @@ embedding's output and are summed into one stream at the end.  The update by
 one branch and the read of the next are one kernel (ops.hyper_step), as the
 pre-norm block's addition lives in the next norm's kernel.
 
+"parallel_residual": the layer's branches all read the same stream, each
+through a norm of its own, and their outputs are added to it together:
+x = x + (mixer(norm1(x)) + ffn(norm2(x))).  The sum of the branches' outputs,
+its addition to the 32-bit residual and the next layer's norms are one
+kernel (ops.PendingSum, ops.add_group_rmsnorm): the norms of one layer differ
+in their weights only, so the row's statistics are computed once.
+
 "reinject" (a stream operation): x <- W [x; x0] with x0 the embedding's
 output, for models that feed the input again at the start of a pass over a
 span of layers.
@@ -54,6 +61,34 @@ class Sandwich(Arrangement):
             h = normed_input(b.norm, b.part, stream)
             y = b.part.forward(h, batch, cache, writes) if b.role == "mixer" else b.part.forward(h, batch)
             stream.pending = ops.PendingNormed(y, b.post_norm.weight, b.post_norm.eps)
+
+
+class ParallelResidual(Arrangement):
+    """Up to two branches side by side on the same stream."""
+
+    def run(self, layer, stream, batch, cache, writes):
+        bs = layer.branches
+        if len(bs) > 2:
+            raise ValueError("the 'parallel_residual' arrangement takes one or two branches")
+        norms = [b.norm for b in bs]
+        same = all(getattr(n, "fuses_pending_sum", False) and hasattr(n, "groups") for n in norms) and len(
+            {(n.groups, n.eps, n.env.dtype) for n in norms}) == 1
+        pending = stream.pending
+        if isinstance(pending, (ops.PendingLinear, ops.PendingNormed)):
+            pending = pending.materialize()
+        if same:
+            hs = ops.add_group_rmsnorm(stream.resid, pending, [n.weight for n in norms], norms[0].groups, norms[0].eps,
+                                       norms[0].env.dtype)
+        else:
+            # norms of different kinds: the first one adds what is pending, the others read the sum
+            hs = []
+            for b in bs:
+                hs.append(normed_input(b.norm, None, stream))
+                stream.pending = None
+        ys = []
+        for b, h in zip(bs, hs):
+            ys.append(b.part.forward(h, batch, cache, writes) if b.role == "mixer" else b.part.forward(h, batch))
+        stream.pending = ops.PendingSum(ys)
 
 
 class HyperWiring:
@@ -143,4 +178,5 @@ class Reinject(StreamOp):
 register_arrangement("prenorm", PreNorm)
 register_arrangement("sandwich", Sandwich)
 register_arrangement("hyper", Hyper)
+register_arrangement("parallel_residual", ParallelResidual)
 register_stream_op("reinject", Reinject)

@@ -16,7 +16,8 @@ from .registry import register_embedding, register_head
 
 
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``, ``hidden_size``, ``name`` (full tensor name)."""
+    """params: ``vocab_size``, ``hidden_size``, ``name`` (full tensor name);
+    optional ``scale``: a constant the rows are multiplied by (32-bit)."""
 
     @classmethod
     def tensor_specs(cls, p, prefix):
@@ -26,9 +27,10 @@ class TokenEmbedding(Embedding):
         super().__init__(p, prefix, env, tensors)
         self.table = tensors.get(p["name"], env.dtype)
         self.vocab_size = p["vocab_size"]
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0
 
     def embed(self, ids):
-        return ops.embedding(ids, self.table)
+        return ops.embedding(ids, self.table, self.scale)
 
 
 class LMHead(Head):

@@ -1,6 +1,6 @@
-"""Dense gated feed-forward: down(silu(gate(x)) * up(x))
-(crates/vllm-models/src/llama/architecture.rs:75-85).  gate and up are one
-matrix here, stacked by rows at load.
+"""Dense gated feed-forward: down(act(gate(x)) * up(x)), act = silu
+(crates/vllm-models/src/llama/architecture.rs:75-85) unless the model names
+another one.  gate and up are one matrix here, stacked by rows at load.
 """
 from __future__ import annotations
 
@@ -14,7 +14,9 @@ from .registry import register_feed_forward
 
 class SwiGLU(FeedForward):
     """params: ``hidden_size``, ``intermediate_size``; optional ``names`` (the
-    gate, up and down matrices' names after the prefix)."""
+    gate, up and down matrices' names after the prefix) and ``activation``
+    ("silu", the default, or "gelu_tanh": the products' fused epilogues are
+    silu's, another activation runs as a kernel of its own)."""
 
     NAMES = ("mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")
 
@@ -30,7 +32,10 @@ class SwiGLU(FeedForward):
         gate, up = tensors.get(n_gate, env.dtype), tensors.get(n_up, env.dtype)
         # bfloat16 with I % 8 == 0: gate and up rows interleaved in blocks of 8, which lets the decode
         # product apply SiLU-mul in its epilogue; otherwise gate rows, then up rows
-        self.interleaved = env.dtype == torch.bfloat16 and p["intermediate_size"] % 8 == 0
+        self.act = p.get("activation") or "silu"
+        if self.act not in ops.GATED_ACTIVATIONS:
+            raise ValueError(f"gated activation {self.act!r} is not known; known: {sorted(ops.GATED_ACTIVATIONS)}")
+        self.interleaved = env.dtype == torch.bfloat16 and p["intermediate_size"] % 8 == 0 and self.act == "silu"
         self.w_gate_up = (ops.interleave_gate_up(gate, up) if self.interleaved
                           else torch.cat([gate, up], dim=0).contiguous())
         tensors.drop(n_gate, n_up)
@@ -40,6 +45,11 @@ class SwiGLU(FeedForward):
     defers_output = True
 
     def forward(self, x, batch, defer=False):
+        if self.act != "silu":
+            if isinstance(x, ops.NormedRows):
+                x = x.materialize()
+            act = ops.gated_activation(ops.linear(x, self.w_gate_up), self.act)
+            return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)
         if isinstance(x, ops.NormedRows):
             if self.interleaved and ops.skinny_scaled_ok(x, self.w_gate_up):
                 act = ops.skinny_gemm_scaled(x, self.w_gate_up, silu_mul=True)   # decode: norm, product and SiLU-mul in one

@@ -19,6 +19,7 @@ from . import attention as _attention, block as _block, embedding as _embedding 
 from . import mlp as _mlp, norm as _norm, rope as _rope  # noqa: F401
 from . import latent_attention as _latent_attention, moe as _moe  # noqa: F401
 from . import talking_attention as _talking_attention, recurrent as _recurrent, parallel as _parallel  # noqa: F401
+from . import state_mixers as _state_mixers  # noqa: F401
 
 
 def _part_registry(role: str):

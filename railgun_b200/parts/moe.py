@@ -28,13 +28,19 @@ class RoutedExperts(FeedForward):
     ``expert_size`` (an expert's inner size), ``shared_size`` (the shared
     expert's, or None), ``base`` (tensor names after the prefix start with it:
     ``<base>e<i>.gate|up|down``, ``<base>router``, ``<base>correction``,
-    ``<base>shared.gate|up|down``)."""
+    ``<base>shared.gate|up|down``).  Optional: ``correction`` False (no
+    correction tensor: the largest scores are chosen), ``renormalize`` False
+    (the weights are the chosen scores themselves), ``activation`` ("silu",
+    "gelu_tanh" or "clamped_swish" with ``limit``: g' sigmoid(1.702 g') (u' + 1),
+    g' = min(g, limit), u' = clamp(u, -limit, limit))."""
 
     @classmethod
     def tensor_specs(cls, p, prefix):
         W, E, N, F = p["hidden_size"], p["experts"], p["experts"] + p["identity"], p["expert_size"]
         b = prefix + p.get("base", "mlp.")
-        out = {b + "router": TensorSpec((N, W)), b + "correction": TensorSpec((N,))}
+        out = {b + "router": TensorSpec((N, W))}
+        if p.get("correction", True):
+            out[b + "correction"] = TensorSpec((N,))
         for e in range(E):
             out[f"{b}e{e}.gate"] = TensorSpec((F, W))
             out[f"{b}e{e}.up"] = TensorSpec((F, W))
@@ -57,7 +63,12 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"{self.top} choices among {self.N} router outputs")
         b = prefix + p.get("base", "mlp.")
         self.router = tensors.get(b + "router", torch.float32)
-        self.correction = tensors.get(b + "correction", torch.float32)
+        self.correction = tensors.get(b + "correction", torch.float32) if p.get("correction", True) else None
+        self.renormalize = bool(p.get("renormalize", True))
+        self.act = p.get("activation") or "silu"
+        self.limit = float(p.get("limit") or 0.0)
+        if self.act not in ops.GATED_ACTIVATIONS:
+            raise ValueError(f"gated activation {self.act!r} is not known; known: {sorted(ops.GATED_ACTIVATIONS)}")
         if self.E:
             self.w_gate_up = torch.stack([torch.cat([tensors.get(f"{b}e{e}.gate", env.dtype),
                                                      tensors.get(f"{b}e{e}.up", env.dtype)], dim=0)
@@ -68,13 +79,14 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, batch):
         T = x.shape[0]
-        ids, weights = ops.moe_route(x, self.router, self.correction, self.top)
+        ids, weights = ops.moe_route(x, self.router, self.correction, self.top, self.renormalize)
         y = pair_pos = None
         if self.E:
             places = T * self.top
             rows = ops.moe_tile_rows(x.dtype, places, self.E, self.w_gate_up.shape[2], self.w_down.shape[2])
             sorted_pair, pair_pos, tiles = ops.moe_align(ids, self.E, rows)
-            act = ops.moe_grouped_gemm(x, sorted_pair, self.top, self.w_gate_up, tiles, places, True, rows)
+            act = ops.moe_grouped_gemm(x, sorted_pair, self.top, self.w_gate_up, tiles, places, True, rows,
+                                       act=self.act, limit=self.limit)
             y = ops.moe_grouped_gemm(act, None, 1, self.w_down, tiles, places, False, rows)
         else:
             pair_pos = ids

@@ -19,7 +19,9 @@ class RMSNorm(Norm):
     """params: ``size``, ``eps``, ``name`` (weight tensor name after the prefix);
     optional ``scale_name`` (a second per-feature vector, a layer scale, that
     multiplies the normed value) and ``mult`` (a constant that does): both are
-    multiplied into the weight at load, in 32-bit."""
+    multiplied into the weight at load, in 32-bit; ``groups`` (default 1): the
+    row is cut into that many equal consecutive parts and each part is divided
+    by its own root mean square."""
 
     @classmethod
     def tensor_specs(cls, params, prefix):
@@ -37,11 +39,19 @@ class RMSNorm(Norm):
         if params.get("mult") is not None and float(params["mult"]) != 1.0:
             self.weight = self.weight * float(params["mult"])
         self.weight = self.weight.contiguous()
+        self.groups = int(params.get("groups") or 1)
+        if self.groups < 1 or int(params["size"]) % self.groups:
+            raise ValueError(f"rows of {params['size']} do not split into {self.groups} equal groups")
 
     fuses_pending_linear = True
     fuses_post_norm = True
+    fuses_pending_sum = True
 
     def add_norm(self, resid, pending, rows=None):
+        if self.groups > 1 or isinstance(pending, ops.PendingSum):
+            if isinstance(pending, (ops.PendingLinear, ops.PendingNormed)):
+                pending = pending.materialize()
+            return ops.add_group_rmsnorm(resid, pending, [self.weight], self.groups, self.eps, self.env.dtype, rows)[0]
         if isinstance(pending, ops.PendingNormed):
             return ops.add_postnorm_rmsnorm(resid, pending, self.weight, self.eps, self.env.dtype, rows)
         if isinstance(pending, ops.PendingLinear):
