@@ -637,6 +637,139 @@ def run_rupulix(args):
     return 0
 
 
+def mepatar_sizes(name):
+    """(Mepatar configuration, the Rupulix configuration of equal width, layer runs and vocabulary beside it)."""
+    def mep(width, heads, kv, d, window, ff, experts, top, eff, vocab):
+        ret = dict(type="retention", mixer=dict(heads=heads, dim=d, vdim=d, rot=dict(base=10000.0, dims=d),
+                                                decay=[1.0 - 2.0 ** (-5 - 0.4 * i) for i in range(heads)]))
+        dlt = dict(type="delta", mixer=dict(heads=heads, kv_heads=heads // 2, dim=d, vdim=d, conv=4))
+        att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=d, vdim=d, scale=d ** -0.5,
+                                                rot=dict(base=10000.0, dims=d // 2), mask=dict(size=window, keep_first=4)))
+        dense = dict(kind="dense", ff=ff)
+        moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=eff, limit=7.0))
+        layers = [dict(ret, mlp=dense), dict(dlt, mlp=moe), dict(att, mlp=moe), dict(ret, mlp=moe), dict(dlt, mlp=dense),
+                  dict(att, mlp=dense)]
+        return dict(architecture="Mepatar", width=width, vocab=vocab, norm=dict(eps=1e-6, groups=4),
+                    embedding=dict(scale=width ** 0.5), canon=dict(taps=4), layers=layers)
+
+    if name == "w2048":      # 16 heads of 128 (2 key/value heads, window 512 keeping 4); 32 experts of 2,048, 4 chosen
+        return mep(2048, 16, 2, 128, 512, 8192, 32, 4, 2048, 32768), rupulix_sizes(name)[0]
+    if name == "w1024":      # 8 heads of 128 (2 key/value heads, window 512 keeping 4); 16 experts of 1,024, 4 chosen
+        return mep(1024, 8, 2, 128, 512, 4096, 16, 4, 1024, 32768), rupulix_sizes(name)[0]
+    raise ValueError(name)
+
+
+def mepatar_decode_bytes(cfg, batch, context):
+    """Bytes a decode step has to read or write: the weights of every layer (of the experts, those that `batch`
+    tokens can reach at most), the head, and what the live requests keep: matrix states in 32-bit (read and
+    written), convolution tails, and an attention layer's cache as far back as its window and kept tokens."""
+    W, V = cfg["width"], cfg["vocab"]
+    K0 = (cfg.get("canon") or {}).get("taps", 0)
+    total = V * W * 2
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if K0:
+            total += batch * (K0 - 1) * W * 4 * 2
+        if L["type"] == "retention":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            total += (2 * H * d + 2 * H * dv) * W * 2 + W * H * dv * 2 + batch * H * d * dv * 4 * 2
+        elif L["type"] == "delta":
+            H, G, d, dv, K = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            total += (2 * G * d + 2 * H * dv + 2 * H) * W * 2 + W * H * dv * 2
+            total += batch * (H * d * dv * 4 * 2 + (K - 1) * (2 * G * d + H * dv) * 4 * 2)
+        else:
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mask = m.get("mask") or {}
+            seen = min(context, mask["size"] + mask.get("keep_first", 0)) if mask.get("size") else context
+            total += ((H + G) * d + G * dv) * W * 2 + W * H * dv * 2 + batch * seen * G * 2 * max(d, dv) * 2
+        f = L["mlp"]
+        if f and f["kind"] == "dense":
+            total += 3 * f["ff"] * W * 2
+        elif f:
+            r, e = f["router"], f["expert"]
+            total += r["experts"] * W * 2 + min(r["experts"], batch * r["top"]) * 3 * e["ff"] * W * 2
+    return total
+
+
+def mepatar_prefill_flops(cfg, T):
+    """FLOPs of one prompt of T tokens by the design's own arithmetic: products, the chosen experts, attention
+    over the keys a query sees, and the matrix states' updates and read-outs (4 d dv per head and token)."""
+    W, V = cfg["width"], cfg["vocab"]
+    total = 2 * V * W
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "retention":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            total += 2 * T * ((2 * H * d + 2 * H * dv) * W + W * H * dv) + T * H * 4 * d * dv
+        elif L["type"] == "delta":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            total += 2 * T * ((2 * G * d + 2 * H * dv + 2 * H) * W + W * H * dv) + T * H * 6 * d * dv
+        else:
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mask = m.get("mask") or {}
+            win, keep = mask.get("size", 0), mask.get("keep_first", 0)
+            pairs = sum(min(t + 1, win + min(keep, max(0, t + 1 - win))) if win else t + 1 for t in range(T))
+            total += 2 * T * (((H + G) * d + G * dv) * W + W * H * dv) + H * 2 * (d + dv) * pairs
+        f = L["mlp"]
+        if f and f["kind"] == "dense":
+            total += 2 * T * 3 * f["ff"] * W
+        elif f:
+            total += 2 * T * (f["router"]["experts"] * W + f["router"]["top"] * 3 * f["expert"]["ff"] * W)
+    return total
+
+
+def run_mepatar(args):
+    """Prefill and decode throughput of Mepatar at layer sizes of real models (random weights), beside Rupulix
+    (the framework's other design with state slots, a window and parallel branches) at equal width, number of
+    layer runs and vocabulary.  One JSON line per model and size."""
+    import numpy as np
+    import torch
+    from railgun_b200.engine.batch import StepEntry
+    from railgun_b200.engine.engine import Engine
+    page, pool_tokens = 16, 64 * 4096
+    pk, pk_src = peaks()
+    for size in (args.sizes.split(",") if args.sizes else ["w1024", "w2048"]):
+        for label, cfg in zip(("mepatar", "rupulix"), mepatar_sizes(size)):
+            mdir = model_folder(cfg)
+            eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
+                         max_num_batched_tokens=8192, max_model_len=4096)
+            runner = eng.runner
+            V = cfg["vocab"]
+            rng = np.random.default_rng(0)
+            _, _, time_decode = decode_tools(runner, V, rng)
+            line = {"mode": "mepatar", "size": size, "model": label, "layer_runs": len(runner.model.order),
+                    "cache_bytes_per_token": runner.cache.bytes_per_token()}
+            for b in (8, 64):
+                tok_s, ms, n_launch, _ = time_decode(b, args.steps, args.warmup, 1000 * b, args.context)
+                line[f"decode_b{b}_tok_s"], line[f"decode_b{b}_ms"] = round(tok_s, 1), round(ms, 4)
+                line[f"decode_b{b}_launches_per_step"] = n_launch // args.steps
+                ctx = args.context + args.warmup + args.steps // 2
+                by = mepatar_decode_bytes(cfg, b, ctx) if label == "mepatar" else rupulix_decode_bytes(cfg, b, ctx)
+                line[f"decode_b{b}_GB_per_step"] = round(by / 1e9, 3)
+                line[f"decode_b{b}_frac_hbm"] = round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
+            prompt = rng.integers(0, V, size=args.tokens).tolist()
+            times = []
+            for i in range(args.warmup + 7):
+                torch.cuda.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                runner.step([StepEntry(7000 + i, prompt, [args.tokens - 1])])
+                t1.record()
+                torch.cuda.synchronize()
+                runner.end([7000 + i])
+                times.append(t0.elapsed_time(t1))
+            runner.check_device_errors()
+            ms = sorted(times[args.warmup:])[len(times[args.warmup:]) // 2]
+            fl = mepatar_prefill_flops(cfg, args.tokens) if label == "mepatar" else rupulix_prefill_flops(cfg, args.tokens)
+            line.update(prefill_tokens=args.tokens, prefill_ms=round(ms, 3), prefill_tok_s=round(args.tokens / ms * 1e3, 1),
+                        prefill_TFLOP=round(fl / 1e12, 3), prefill_frac_flops=round(fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                        peaks=pk_src)
+            print(json.dumps(line), flush=True)
+            del eng, runner, time_decode
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_kernels(args):
     """Times the hot kernels one by one, each as a CUDA graph of 16 calls over 16 different operand sets (so
     that weights and caches come from HBM, not L2), with CUDA events around replays.  One JSON line per case."""
@@ -920,6 +1053,88 @@ def run_kernels(args):
                 conv_frac=round(by_c / us_c / 1e3 / pk["hbm_gbs"], 3), gates_product_us=round(us_g, 2),
                 gates_TFLOPs=round(2 * T * C * 2 * (C // Bk) / us_g / 1e6, 2), gates_product_bf16_halves_us=round(us_h, 2), scan_us=round(us_s, 2),
                 scan_frac=round(by_s / us_s / 1e3 / pk["hbm_gbs"], 3))
+    if on("mepatar_rows"):
+        # Mepatar's own kernels by the bytes they have to move (and, for the matrix states, the 32-bit work they
+        # have to do), each beside the like kernel of another design: the norm in groups beside add + RMSNorm, the
+        # input convolution beside the recurrence's convolution, the state scans beside the recurrence's scan,
+        # attention that keeps the first tokens beside the same kernel with a plain window
+        from types import SimpleNamespace
+        pk, _ = peaks()
+        fp32_tflops = 148 * 128 * 2 * 1.9e9 / 1e12          # FMA lanes x 2 x the clock under load
+        W, Hh, Hq, dd, K, G = 2048, 16, 8, 128, 4, 2
+        for T in (64, 4096):
+            R_ = 1 if T > 64 else T
+            per = T // R_
+            batch = SimpleNamespace(cu_seqlens=torch.arange(0, T + 1, per, dtype=torch.int32, device=dev),
+                                    num_requests=R_, req_of_token=(torch.arange(T, device=dev) // per).to(torch.int32),
+                                    start_pos=torch.full((R_,), 1000, dtype=torch.int32, device=dev),
+                                    state_slots=torch.arange(R_, dtype=torch.int32, device=dev), max_query_len=per,
+                                    positions=(1000 + torch.arange(T, device=dev) % per).to(torch.int32))
+            rs = [torch.randn(T, W, device=dev) for _ in range(L)]
+            ys = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(L)]
+            nw, nw2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+            us = timed(lambda: [ops.add_group_rmsnorm(r, y, [nw, nw2], 4, 1e-6, torch.bfloat16) for r, y in zip(rs, ys)])
+            us2 = timed(lambda: [ops.add_rmsnorm(r, y, nw, 1e-6, torch.bfloat16) for r, y in zip(rs, ys)])
+            by, by2 = T * W * (8 + 2 + 4), T * W * (8 + 2 + 2)
+            out(f"norm in 4 groups, two outputs W{W} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
+                add_rmsnorm_us=round(us2, 2), add_rmsnorm_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))
+            taps = torch.randn(W, K, device=dev) * 0.3
+            cstate = [torch.randn(R_, K - 1, W, device=dev) for _ in range(L)]
+            us = timed(lambda: [(ops.causal_conv(y, 0, taps, c, batch, torch.bfloat16, residual=True),
+                                 ops.conv_state_update(y, 0, c, batch)) for y, c in zip(ys, cstate)])
+            by = T * W * (2 + 2) + R_ * (K - 1) * W * 8
+            out(f"input convolution taps{K} W{W} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3))
+            qs = [torch.randn(T, Hq * dd, device=dev) * 0.1 for _ in range(L)]
+            ks = [torch.nn.functional.normalize(torch.randn(T, Hq, dd, device=dev), dim=-1).view(T, Hq * dd) for _ in range(L)]
+            vs = [torch.randn(T, Hh * dd, device=dev).to(torch.bfloat16) for _ in range(L)]
+            sts = [torch.zeros(R_, Hh, dd, dd, device=dev) for _ in range(L)]      # [slots, H, dv, d]
+            gg, bb = torch.rand(T, Hh, device=dev) * 0.1 + 0.9, torch.rand(T, Hh, device=dev)
+            decay = torch.full((Hh,), 0.99, device=dev)
+            q16 = [torch.randn(T, Hh * dd, device=dev) * 0.1 for _ in range(L)]
+            k16 = [torch.randn(T, Hh * dd, device=dev) * 0.1 for _ in range(L)]
+            us_r = timed(lambda: [ops.state_scan(q, k, v, st, batch, Hh, dd, dd, decay=decay)
+                                  for q, k, v, st in zip(q16, k16, vs, sts)])
+            us_d = timed(lambda: [ops.state_scan(q, k, v, st, batch, Hh, dd, dd, g=gg, beta=bb)
+                                  for q, k, v, st in zip(qs, ks, vs, sts)])
+            by_r = T * (2 * Hh * dd * 4 + Hh * dd * (2 + 4)) + R_ * Hh * dd * dd * 8
+            by_d = T * (2 * Hq * dd * 4 + Hh * dd * (2 + 4)) + R_ * Hh * dd * dd * 8
+            out(f"state scans H{Hh} d{dd} dv{dd} T{T} ({R_} requests)", us_r + us_d, retention_us=round(us_r, 2),
+                retention_frac_hbm=round(by_r / us_r / 1e3 / pk["hbm_gbs"], 3),
+                retention_frac_fp32=round(T * Hh * 6 * dd * dd / us_r / 1e6 / fp32_tflops, 3), delta_us=round(us_d, 2),
+                delta_frac_hbm=round(by_d / us_d / 1e3 / pk["hbm_gbs"], 3),
+                delta_frac_fp32=round(T * Hh * 6 * dd * dd / us_d / 1e6 / fp32_tflops, 3))
+            os_ = [torch.randn(T, Hh, dd, device=dev) for _ in range(L)]
+            us = timed(lambda: [ops.head_norm_gate(o, v, nw[:dd], 1e-6, torch.bfloat16) for o, v in zip(os_, vs)])
+            by = T * Hh * dd * (4 + 2 + 2)
+            out(f"heads' norm and gate H{Hh} dv{dd} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3))
+        # attention over a window of 512 that keeps the first 4 tokens: 64 single tokens at context 4,096, and a prompt
+        for T, B in ((64, 64), (4096, 1)):
+            ctx = 4096
+            blocks = -(-ctx // page)
+            kvs = [torch.randn(B * blocks, 2, G, page, dd, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(B * blocks, dtype=torch.int32, device=dev).view(B, blocks).contiguous()
+            q = (torch.randn(T, Hh * dd, device=dev) * dd ** -0.5).to(torch.bfloat16)
+            req = (torch.arange(T, device=dev) // (T // B)).to(torch.int32)
+            pos = (torch.arange(T, device=dev) % (T // B) + (ctx - T // B)).to(torch.int32)
+            o = torch.empty(T, Hh * dd, dtype=torch.bfloat16, device=dev)
+            res = {}
+            for keep in (4, 0):
+                if B > 1:
+                    splits = ops.decode_splits(T, G * (-(-(Hh // G) // 8)), 512 + keep)
+                    res[keep] = timed(lambda: [ops.decode_attention(q, Hh * dd, o, kv, bt, None, T, req, pos, Hh, G, dd, 512, 1.0,
+                                                                    splits, keep_first=keep) for kv in kvs])
+                else:
+                    t64 = torch.tensor([(k, min(64, T - k), 0) for k in range(0, T, 64)], dtype=torch.int32, device=dev)
+                    res[keep] = timed(lambda: [ops.prefill_attention(q, Hh * dd, o, kv, bt, t64, pos, Hh, G, dd, 512, 1.0,
+                                                                     keep_first=keep) for kv in kvs])
+            seen = sum(min(int(p) + 1, 516) for p in pos.tolist())
+            by = (B * 516 * G * 2 * dd * 2) if B > 1 else 0
+            fl = Hh * 4 * dd * seen
+            out(f"attention window 512 keeping 4, H{Hh} G{G} d{dd}, {B} requests x {T // B} tokens", res[4],
+                plain_window_us=round(res[0], 2), TFLOPs=round(fl / res[4] / 1e6, 2),
+                **({"frac_hbm": round(by / res[4] / 1e3 / pk["hbm_gbs"], 3), "plain_window_frac_hbm": round(
+                    (B * 512 * G * 2 * dd * 2) / res[0] / 1e3 / pk["hbm_gbs"], 3)} if B > 1 else
+                   {"frac_flops": round(fl / res[4] / 1e6 / pk["bf16_tflops"], 3)}))
     if on("moe"):
         # the routed experts' two grouped products (32 experts of 1,024 at width 2,048, 4 choices) beside the dense
         # model's gate|up and down products of equal work: decode by bytes of weights read, prompts by FLOP/s
@@ -967,11 +1182,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar", "rupulix"],
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar", "rupulix", "mepatar"],
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
                          "kernels: the hot kernels one by one; dizatar / rupulix: prefill and decode of the Dizatar / Rupulix design at "
-                         "layer sizes of real models beside the dense model of equal width")
-    ap.add_argument("--sizes", default="", help="--mode dizatar / rupulix: comma-separated subset of w1024, w2048")
+                         "layer sizes of real models beside the dense model of equal width; mepatar: the same for "
+                         "the Mepatar design beside Rupulix")
+    ap.add_argument("--sizes", default="", help="--mode dizatar / rupulix / mepatar: comma-separated subset of w1024, w2048")
     ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
                     "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives, latent_attention, moe")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
@@ -994,6 +1210,8 @@ def main():
         return run_dizatar(args)
     if args.mode == "rupulix":
         return run_rupulix(args)
+    if args.mode == "mepatar":
+        return run_mepatar(args)
     return run_ours(args)
 
 

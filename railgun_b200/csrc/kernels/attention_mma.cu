@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 64 ? 4 : (DMAX <= 128 ? 2 : 
 prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ kv_cache, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tiles, const int* __restrict__ positions, int nh, int nkv, int d_arg,
-                         int page_size, int page_shift, int window, float scale_log2) {
+                         int page_size, int page_shift, int window, int keep, float scale_log2) {
     const int d = EXACT ? DMAX : d_arg;
     constexpr int KD = DMAX / 16;          // k-steps over the head dimension
     constexpr int ND = DMAX / 8;           // n-tiles of the output
@@ -145,7 +145,15 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     const int p0 = positions[row0];
     const int hi = p0 + nrows - 1;                                 // last key any row of the tile attends
     const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
-    const int kt0 = lo / BN, kt1 = hi / BN;
+    int kt0 = lo / BN;
+    const int kt1 = hi / BN;
+    // keep: with a window, the request's first `keep` tokens stay visible.  Their nk tiles come first, then the
+    // window's: the loop runs over tile numbers vt = kt0 - nk .. kt1, of which those below kt0 stand for tiles
+    // 0 .. nk - 1.  Where the window's first tile touches the kept ones it is one run from tile 0.
+    int nk = (window > 0 && keep > 0) ? (keep + BN - 1) / BN : 0;
+    if (kt0 <= nk) { kt0 = 0; nk = 0; }
+    const int gap = kt0 - nk, v0 = kt0 - nk;
+    auto phys = [&](int vt) { return vt >= kt0 ? vt : vt - gap; };
     const int d16 = d >> 4, d8 = d >> 3;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -164,10 +172,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     const size_t page_elems = (size_t)2 * nkv * page_size * d;
     const int v_off = nkv * page_size * d;
     int page_next[KD];
-    tg.pages(bt, kt0 * BN, hi + 1, page_next);
-    tg.issue(sKV, sKV + BN * stride, kv_cache, page_next, kt0 * BN, page_elems, v_off);
+    tg.pages(bt, phys(v0) * BN, hi + 1, page_next);
+    tg.issue(sKV, sKV + BN * stride, kv_cache, page_next, phys(v0) * BN, page_elems, v_off);
     cp_async_commit();
-    tg.pages(bt, (kt0 + 1) * BN, hi + 1, page_next);               // beyond the last key: all -1
+    tg.pages(bt, phys(v0 + 1) * BN, hi + 1, page_next);            // beyond the last key: all -1
 
     uint32_t qf[Q_IN_REGS ? KD : 1][4];
     float o[ND][4];
@@ -181,21 +189,22 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     const int b_key = (lane & 7) + (lane >> 4) * 8, b_dim = ((lane >> 3) & 1) * 8;          // K as B operand
     const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_dim = (lane >> 4) * 8;          // V as B operand (.trans)
 
-    for (int kt = kt0; kt <= kt1; ++kt) {
-        const int stage = (kt - kt0) & 1;
+    for (int vt = v0; vt <= kt1; ++vt) {
+        const int kt = phys(vt);
+        const int stage = (vt - v0) & 1;
         bf16* sK = sKV + stage * stage_elems;
         bf16* sV = sK + BN * stride;
-        if (kt + 1 <= kt1) {
+        if (vt + 1 <= kt1) {
             bf16* nK = sKV + (stage ^ 1) * stage_elems;
-            tg.issue(nK, nK + BN * stride, kv_cache, page_next, (kt + 1) * BN, page_elems, v_off);
+            tg.issue(nK, nK + BN * stride, kv_cache, page_next, phys(vt + 1) * BN, page_elems, v_off);
             cp_async_commit();
-            tg.pages(bt, (kt + 2) * BN, hi + 1, page_next);
+            tg.pages(bt, phys(vt + 2) * BN, hi + 1, page_next);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (Q_IN_REGS && kt == kt0) {
+        if (Q_IN_REGS && vt == v0) {
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd)
                 if (kd < d16) ldmatrix_x4(qf[kd], sQ + a_row * stride + kd * 16 + a_col);
@@ -203,7 +212,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         // this warp's rows attend nothing in this tile?  (all keys after its last row, or before its first row's window)
         const int key_base = kt * BN;
         const int wfirst = p0 + warp * 16, wlast = wfirst + 15;      // warp-uniform: every lane takes the same branch
-        const bool skip = key_base > wlast || (window > 0 && key_base + BN - 1 < wfirst - window + 1);
+        const bool skip = key_base > wlast || (window > 0 && key_base + BN - 1 < wfirst - window + 1 && key_base >= keep);
         if (!skip) {
             float s[BN / 8][4];
 #pragma unroll
@@ -234,7 +243,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                     if (edge) {
                         const int key = key_base + j * 8 + tq * 2 + (e & 1);
                         const int prow = (e < 2) ? prow0 : prow1;
-                        if (!(key <= prow && (window <= 0 || key > prow - window))) v = -INFINITY;
+                        if (!(key <= prow && (window <= 0 || key > prow - window || key < keep))) v = -INFINITY;
                     }
                     s[j][e] = v;
                     if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
@@ -323,7 +332,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                         const int* __restrict__ req_of_token, const int* __restrict__ positions,
                         float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
                         int* __restrict__ counters, int nh, int nkv, int d_arg,
-                        int page_size, int page_shift, int window, float scale_log2, int num_splits,
+                        int page_size, int page_shift, int window, int keep, float scale_log2, int num_splits,
                         int head_tiles, int cluster_merge) {
     const int d = EXACT ? DMAX : d_arg;
     __shared__ int is_last;
@@ -353,10 +362,16 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     const int pos = positions[t];
     const int* bt = block_table + (size_t)r * max_blocks;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int lo_al = (lo / BN) * BN;
-    const int n_keys = pos + 1 - lo_al;
+    int lo_al = (lo / BN) * BN;
+    // keep: with a window, the request's first `keep` tokens stay visible.  Their tiles (kept_al keys) come first
+    // in the splits' key numbers, directly before the window's first tile: a key number below lo_al stands for
+    // the key `shift` places earlier.  Where the window's first tile touches the kept ones it is one run from 0.
+    int kept_al = (window > 0 && keep > 0) ? (keep + BN - 1) / BN * BN : 0;
+    if (lo_al <= kept_al) { lo_al = 0; kept_al = 0; }
+    const int shift = lo_al - kept_al;
+    const int n_keys = pos + 1 - shift;
     const int per_split = ((n_keys + num_splits - 1) / num_splits + BN - 1) / BN * BN;
-    const int k_begin = lo_al + split * per_split;
+    const int k_begin = shift + split * per_split;
     const int k_end = min(pos + 1, k_begin + per_split);
     const int d16 = d >> 4, d8 = d >> 3;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -454,26 +469,30 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
 #pragma unroll
     for (int j = 0; j < KD; ++j) g_dst[j] = g_row[j] * stride + g_col[j];
     auto pages_of = [&](int key0, int (&pg)[KD]) {                 // page of every piece's row (-1: no such key)
+        const int back = key0 < lo_al ? shift : 0;                  // a tile of the kept first tokens
         if (one_page) {
             const int key = key0 + warp * 16;                      // the same page for the whole warp
-            pg[0] = key < k_end ? bt[key >> page_shift] : -1;
+            pg[0] = key < k_end ? bt[(key - back) >> page_shift] : -1;
             return;
         }
 #pragma unroll
         for (int j = 0; j < KD; ++j) {
             const int key = key0 + warp * 16 + g_row[j];
-            pg[j] = (g_row[j] >= 0 && key < k_end) ? bt[page_shift >= 0 ? key >> page_shift : key / page_size] : -1;
+            const int pk = key - back;
+            pg[j] = (g_row[j] >= 0 && key < k_end) ? bt[page_shift >= 0 ? pk >> page_shift : pk / page_size] : -1;
         }
     };
     auto gather = [&](int stage, const int (&pg)[KD], int key0) {
         bf16* sK = sKV + stage * stage_elems + warp * 16 * stride;
         bf16* sV = sK + BN * stride;
+        const int back = key0 < lo_al ? shift : 0;
         if (one_page) {
             const int key = key0 + warp * 16;
             const bool page_ok = pg[0] >= 0;
             const bf16* base = kv_cache;
             if (page_ok)
-                base = kv_cache + (size_t)pg[0] * page_elems + ((size_t)kvh * page_size + (key & (page_size - 1))) * d;
+                base = kv_cache + (size_t)pg[0] * page_elems +
+                       ((size_t)kvh * page_size + ((key - back) & (page_size - 1))) * d;
             const int rows_ok = k_end - key;                        // rows at or beyond it are zero-filled
 #pragma unroll
             for (int j = 0; j < KD; ++j) {
@@ -492,7 +511,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                 const bool valid = pg[j] >= 0;
                 const bf16* ksrc = kv_cache;
                 if (valid) {
-                    const int key = key0 + warp * 16 + g_row[j];
+                    const int key = key0 + warp * 16 + g_row[j] - back;
                     const int off = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
                     ksrc = kv_cache + (size_t)pg[j] * page_elems + ((size_t)kvh * page_size + off) * d + g_col[j];
                 }
@@ -561,8 +580,9 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             cp_async_wait<DEC_STAGES - 1>();
         }
         __syncwarp();
-        const int key_base = k_begin + it * BN + warp * 16;          // this warp's 16 keys
-        if (key_base < k_end && key_base + 15 >= lo) {
+        const int key_base = k_begin + it * BN + warp * 16;          // this warp's 16 keys (as the splits number them)
+        const int pkb = key_base < lo_al ? key_base - shift : key_base;   // and where they are in the request
+        if (key_base < k_end && (pkb + 15 >= lo || pkb < keep)) {
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd) {
@@ -577,12 +597,12 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             }
             // head g, keys key_base + 2 tq + {0, 1} (s0) and + 8 (s1); rows 8..15 of the tile are padding
             float v00 = s0[0] * scale_log2, v01 = s0[1] * scale_log2, v10 = s1[0] * scale_log2, v11 = s1[1] * scale_log2;
-            if (key_base + 16 > k_end || key_base < lo) {            // an edge tile: some of its keys are not attended
-                const int k0 = key_base + tq * 2;
-                if (!(k0 < k_end && k0 >= lo)) v00 = -INFINITY;
-                if (!(k0 + 1 < k_end && k0 + 1 >= lo)) v01 = -INFINITY;
-                if (!(k0 + 8 < k_end && k0 + 8 >= lo)) v10 = -INFINITY;
-                if (!(k0 + 9 < k_end && k0 + 9 >= lo)) v11 = -INFINITY;
+            if (key_base + 16 > k_end || pkb < lo) {                 // an edge tile: some of its keys are not attended
+                const int k0 = key_base + tq * 2, p0 = pkb + tq * 2;
+                if (!(k0 < k_end && (p0 >= lo || p0 < keep))) v00 = -INFINITY;
+                if (!(k0 + 1 < k_end && (p0 + 1 >= lo || p0 + 1 < keep))) v01 = -INFINITY;
+                if (!(k0 + 8 < k_end && (p0 + 8 >= lo || p0 + 8 < keep))) v10 = -INFINITY;
+                if (!(k0 + 9 < k_end && (p0 + 9 >= lo || p0 + 9 < keep))) v11 = -INFINITY;
             }
             float mx = fmaxf(fmaxf(v00, v01), fmaxf(v10, v11));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -702,11 +722,13 @@ template <typename K> static int allow_smem(K kernel, size_t bytes) {
     return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, const void* kv_cache,
-                                    const int* block_table, int max_blocks, const int* tiles, int n_tiles,
-                                    const int* positions, int nh, int nkv, int d, int page_size, int window,
-                                    float scale, void* stream) {
+// keep_first: with a window, the first positions of a request that every later query still sees
+extern "C" int rg_prefill_attention_keep(const void* q, int q_stride, void* out, const void* kv_cache,
+                                         const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                                         const int* positions, int nh, int nkv, int d, int page_size, int window,
+                                         int keep_first, float scale, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (keep_first < 0) return RG_ERR_UNSUPPORTED;
     if (d % 16 || d < 16 || d > 256 || nkv < 1 || nh < nkv || nh % nkv || (long long)n_tiles * nh > 0x7fffffffll)
         return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -718,17 +740,25 @@ extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, cons
 #define RG_PREFILL(DM, EX) { int e = allow_smem(prefill_attention_kernel<DM, EX>, smem); if (e) return e; \
     return rg_launch(prefill_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
         (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, page_shift, \
-        window, scale_log2); }
+        window, window > 0 ? keep_first : 0, scale_log2); }
     if (d == 64) RG_PREFILL(64, true) else if (d == 128) RG_PREFILL(128, true)
     else if (d < 64) RG_PREFILL(64, false) else if (d < 128) RG_PREFILL(128, false) else RG_PREFILL(256, false)
 #undef RG_PREFILL
+}
+
+extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, const void* kv_cache,
+                                    const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                                    const int* positions, int nh, int nkv, int d, int page_size, int window,
+                                    float scale, void* stream) {
+    return rg_prefill_attention_keep(q, q_stride, out, kv_cache, block_table, max_blocks, tiles, n_tiles, positions, nh,
+                                     nkv, d, page_size, window, 0, scale, stream);
 }
 
 static int rg_decode_attention_any(const void* q, int q_stride, void* out, const void* kv_cache,
                                    const int* block_table, int max_blocks, const int* rows, int n_tokens,
                                    const int* req_of_token, const int* positions, float* part_o, float* part_ml,
                                    int* counters, int nh, int nkv, int d, int page_size, int window, float scale,
-                                   int num_splits, int cluster_merge, void* stream);
+                                   int num_splits, int cluster_merge, void* stream, int keep_first = 0);
 
 // Scratch the caller provides: part_o floats = n_tokens * nh * num_splits * d; part_ml = n_tokens * nh * num_splits * 2.
 // counters: NULL (a second kernel reduces the splits), or n_tokens * nkv * ceil(group / 8) ints that are zero on
@@ -741,6 +771,18 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
     return rg_decode_attention_any(q, q_stride, out, kv_cache, block_table, max_blocks, rows, n_tokens, req_of_token,
                                    positions, part_o, part_ml, counters, nh, nkv, d, page_size, window, scale, num_splits,
                                    0, stream);
+}
+
+// keep_first: with a window, the first positions of a request that every later query still sees
+extern "C" int rg_decode_attention_keep(const void* q, int q_stride, void* out, const void* kv_cache,
+                                        const int* block_table, int max_blocks, const int* rows, int n_tokens,
+                                        const int* req_of_token, const int* positions, float* part_o, float* part_ml,
+                                        int* counters, int nh, int nkv, int d, int page_size, int window,
+                                        int keep_first, float scale, int num_splits, void* stream) {
+    if (keep_first < 0) return RG_ERR_UNSUPPORTED;
+    return rg_decode_attention_any(q, q_stride, out, kv_cache, block_table, max_blocks, rows, n_tokens, req_of_token,
+                                   positions, part_o, part_ml, counters, nh, nkv, d, page_size, window, scale, num_splits,
+                                   0, stream, keep_first);
 }
 
 // The same with the splits of every (token, head tile) as one thread-block cluster (2 to 8 splits): no scratch, no
@@ -763,7 +805,7 @@ static int rg_decode_attention_any(const void* q, int q_stride, void* out, const
                                    const int* block_table, int max_blocks, const int* rows, int n_tokens,
                                    const int* req_of_token, const int* positions, float* part_o, float* part_ml,
                                    int* counters, int nh, int nkv, int d, int page_size, int window, float scale,
-                                   int num_splits, int cluster_merge, void* stream) {
+                                   int num_splits, int cluster_merge, void* stream, int keep_first) {
     if (n_tokens <= 0) return 0;
     if (d % 16 || d < 16 || d > 256 || nkv < 1 || nh < nkv || nh % nkv || num_splits < 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -781,7 +823,8 @@ static int rg_decode_attention_any(const void* q, int q_stride, void* out, const
     e = rg_launch(decode_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, cluster_merge ? num_splits : 1, \
         (const bf16*)q, q_stride, \
         (const bf16*)kv_cache, block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, (bf16*)out, \
-        counters, nh, nkv, d, page_size, page_shift, window, scale_log2, num_splits, head_tiles, cluster_merge); }
+        counters, nh, nkv, d, page_size, page_shift, window, window > 0 ? keep_first : 0, scale_log2, num_splits, \
+        head_tiles, cluster_merge); }
     if (d == 64) RG_DECODE(64, true) else if (d == 128) RG_DECODE(128, true)
     else if (d < 64) RG_DECODE(64, false) else if (d < 128) RG_DECODE(128, false) else RG_DECODE(256, false)
 #undef RG_DECODE

@@ -204,130 +204,279 @@ extern "C" int rg_delta_prepare(float* qk, int ld, int G, int d, float q_scale, 
     return RG_ERR_UNSUPPORTED;
 }
 
-// One block per (request, head).  Thread (j, part) holds DPER rows of column j of S: rows part * DPER ...; the
-// `parts` threads of a column are neighbouring lanes and add their shares with shuffles.  Tokens are staged in
-// shared memory SCAN_CHUNK at a time.  q, k: [T, Hqk, d] float rows q_ld / k_ld apart; head h reads q/k head
-// h / (H / Hqk).  v: rows v_ld apart (float or bfloat16), head h at column h dv.  decay [H] (retention) or g, beta [T, H]
-// (delta rule; beta null: retention).  state [slots, H, d, dv].  o [T, H, dv] float.
-#define SCAN_CHUNK 16
-template <int DPER, typename V>
-__global__ void state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ k, int k_ld,
-                                  const V* __restrict__ v, int v_ld, const float* __restrict__ decay,
-                                  const float* __restrict__ g, const float* __restrict__ beta,
-                                  float* __restrict__ state, const int* __restrict__ cu_seqlens,
-                                  const int* __restrict__ start_pos, const int* __restrict__ slots,
-                                  float* __restrict__ o, int H, int Hqk, int d, int dv, int parts) {
-    extern __shared__ float sm[];
-    float* sq = sm;                                  // [CHUNK][d]
-    float* sk = sq + SCAN_CHUNK * d;                 // [CHUNK][d]
-    float* sv = sk + SCAN_CHUNK * d;                 // [CHUNK][dv]
-    float* sg = sv + SCAN_CHUNK * dv;                // [CHUNK]
-    float* sb = sg + SCAN_CHUNK;                     // [CHUNK]
+// One block per (request, head, group of CB columns of S).  Thread (j, part) holds DPER rows of column j of S, four
+// at a time: rows 4 (i PARTS + part) ... + 3 for i = 0 .. DPER / 4 - 1, so that the PARTS threads of a column, which
+// are neighbouring lanes and add their shares with shuffles, read neighbouring 16 bytes of a k or q row (no bank
+// conflicts) and of the column's state.  The
+// columns of S never meet (S^T k and S^T q are sums down a column), so a head's columns are spread over blocks.
+// Tokens are staged in shared memory `chunk` at a time, the next chunk on its way (cp.async for q and k, registers
+// for v, g and beta) while this one is worked on; q and k rows are padded with zeros to parts * DPER numbers (rows
+// of S beyond d then stay zero without a test in the loop).  q, k: [T, Hqk, d] float rows q_ld / k_ld apart; head h
+// reads q/k head h / (H / Hqk).  v: rows v_ld apart (float or bfloat16), head h at column h dv.  decay [H]
+// (retention) or g, beta [T, H] (delta rule; beta null: retention).  state [slots, H, dv, d]: S transposed, a
+// thread's rows side by side.  o [T, H, dv] float.
+//
+// The delta rule per token, with a = S_old^T k, b = S_old^T q (one pass over S, reduced together) and c = k . q:
+//   u = beta (v - g a);  o = g b + u c;  S <- g S + k u^T
+// (c once per token and block, when its chunk has arrived) which is S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with one reduction in the chain from token
+// to token instead of two.  Retention: o = decay b + v c;  S <- decay S + k v^T.
+#define SCAN_THREADS 128
+#define SCAN_MAX_PREFETCH 4       // v numbers of the next chunk a thread holds: chunk * CB <= 4 * threads of the block
+
+__device__ __forceinline__ void scan_cp_async4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void scan_cp_async16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src));
+}
+
+template <int DPER, int PARTS, bool DELTA, typename V>
+__global__ void __launch_bounds__(SCAN_THREADS)
+state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ k, int k_ld,
+                  const V* __restrict__ v, int v_ld, const float* __restrict__ decay,
+                  const float* __restrict__ g, const float* __restrict__ beta,
+                  float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                  const int* __restrict__ start_pos, const int* __restrict__ slots,
+                  float* __restrict__ o, int H, int Hqk, int d, int dv, int CB, int chunk, int vec) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int parts = PARTS;
+    constexpr int DP = PARTS * DPER;                 // padded length of a q or k row
+    const int stage = chunk * (2 * DP + CB + 3);     // floats of one stage: q, k [chunk][DP], v [chunk][CB], g, beta, c
     pdl_wait();
     pdl_trigger();
-    const int r = blockIdx.x, h = blockIdx.y;
+    const int r = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * CB;
     const int hq = h / (H / Hqk);
     const int lo = cu_seqlens[r], hi = cu_seqlens[r + 1];
     if (hi <= lo) return;
     const int slot = slots[r];
     const bool has_past = slot >= 0 && start_pos[r] > 0;
-    const int j = threadIdx.x / parts, part = threadIdx.x - j * parts;
-    const bool live = j < dv;
-    const int d0 = part * DPER;
-    float* st = slot >= 0 ? state + ((size_t)slot * H + h) * d * dv : nullptr;
+    const int jl = threadIdx.x / parts, part = threadIdx.x - jl * parts;
+    const int j = j0 + jl;
+    const bool live = jl < CB && j < dv;
+    float* st = (slot >= 0 && live) ? state + (((size_t)slot * H + h) * dv + j) * d : nullptr;   // the column's d numbers
     float S[DPER];
 #pragma unroll
-    for (int i = 0; i < DPER; ++i)
-        S[i] = (has_past && live && d0 + i < d) ? st[(size_t)(d0 + i) * dv + j] : 0.f;
-    const float fixed = decay ? decay[h] : 1.f;
-    for (int base = lo; base < hi; base += SCAN_CHUNK) {
-        const int n = min(SCAN_CHUNK, hi - base);
-        __syncthreads();
-        for (int e = threadIdx.x; e < n * d; e += blockDim.x) {
-            const int tt = e / d, i = e - tt * d;
-            sq[e] = q[(size_t)(base + tt) * q_ld + (size_t)hq * d + i];
-            sk[e] = k[(size_t)(base + tt) * k_ld + (size_t)hq * d + i];
-        }
-        for (int e = threadIdx.x; e < n * dv; e += blockDim.x) {
-            const int tt = e / dv, i = e - tt * dv;
-            sv[e] = to_f32(v[(size_t)(base + tt) * v_ld + (size_t)h * dv + i]);
-        }
-        for (int e = threadIdx.x; e < n; e += blockDim.x) {
-            sg[e] = g ? g[(size_t)(base + e) * H + h] : fixed;
-            sb[e] = beta ? beta[(size_t)(base + e) * H + h] : 0.f;
-        }
-        __syncthreads();
-        for (int tt = 0; tt < n; ++tt) {
-            const float* kt = sk + tt * d + d0;
-            const float* qt = sq + tt * d + d0;
-            const float gt = sg[tt];
-            float u = live ? sv[tt * dv + j] : 0.f;
-            if (beta) {
-                float dot = 0.f;
+    for (int i4 = 0; i4 < DPER / 4; ++i4) {
+        const int r0 = 4 * (i4 * PARTS + part);
+        if (st && has_past && vec && r0 < d) {
+            const float4 x = *reinterpret_cast<const float4*>(st + r0);
+            S[4 * i4] = x.x; S[4 * i4 + 1] = x.y; S[4 * i4 + 2] = x.z; S[4 * i4 + 3] = x.w;
+        } else {
 #pragma unroll
-                for (int i = 0; i < DPER; ++i) {
-                    S[i] *= gt;
-                    if (d0 + i < d) dot += S[i] * kt[i];
+            for (int i = 0; i < 4; ++i) S[4 * i4 + i] = (st && has_past && r0 + i < d) ? st[r0 + i] : 0.f;
+        }
+    }
+    const float fixed = decay ? decay[h] : 1.f;
+    const int ncols = min(CB, dv - j0);
+    // the padding of q and k rows is zero in both stages, once
+    if (DP > d) {
+        for (int e = threadIdx.x; e < 2 * chunk * (DP - d); e += blockDim.x) {
+            const int stg = e / (chunk * (DP - d)), rem = e - stg * chunk * (DP - d);
+            const int tt = rem / (DP - d), i = d + rem - tt * (DP - d);
+            sm[stg * stage + tt * DP + i] = 0.f;
+            sm[stg * stage + chunk * DP + tt * DP + i] = 0.f;
+        }
+    }
+    float pv[SCAN_MAX_PREFETCH], pg = 0.f, pb = 0.f;
+    // q and k of `n` tokens from `base` on into stage `stg`, asynchronously
+    auto issue = [&](int stg, int base, int n) {
+        float* sq = sm + stg * stage;
+        float* sk = sq + chunk * DP;
+        if (vec) {
+            const int d4 = d >> 2;
+            for (int e = threadIdx.x; e < n * d4; e += blockDim.x) {
+                const int tt = e / d4, i = (e - tt * d4) * 4;
+                scan_cp_async16(sq + tt * DP + i, q + (size_t)(base + tt) * q_ld + (size_t)hq * d + i);
+                scan_cp_async16(sk + tt * DP + i, k + (size_t)(base + tt) * k_ld + (size_t)hq * d + i);
+            }
+        } else {
+            for (int e = threadIdx.x; e < n * d; e += blockDim.x) {
+                const int tt = e / d, i = e - tt * d;
+                scan_cp_async4(sq + tt * DP + i, q + (size_t)(base + tt) * q_ld + (size_t)hq * d + i);
+                scan_cp_async4(sk + tt * DP + i, k + (size_t)(base + tt) * k_ld + (size_t)hq * d + i);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    // v, g and beta of those tokens into registers; `park` leaves them in the stage
+    auto fetch = [&](int base, int n) {
+#pragma unroll
+        for (int x = 0; x < SCAN_MAX_PREFETCH; ++x) {
+            const int e = threadIdx.x + x * blockDim.x;
+            if (e < n * ncols) {
+                const int tt = e / ncols, i = e - tt * ncols;
+                pv[x] = to_f32(v[(size_t)(base + tt) * v_ld + (size_t)h * dv + j0 + i]);
+            }
+        }
+        if ((int)threadIdx.x < n) {
+            pg = g ? g[(size_t)(base + threadIdx.x) * H + h] : fixed;
+            pb = beta ? beta[(size_t)(base + threadIdx.x) * H + h] : 0.f;
+        }
+    };
+    auto park = [&](int stg, int n) {
+        float* sv = sm + stg * stage + 2 * chunk * DP;
+#pragma unroll
+        for (int x = 0; x < SCAN_MAX_PREFETCH; ++x) {
+            const int e = threadIdx.x + x * blockDim.x;
+            if (e < n * ncols) {
+                const int tt = e / ncols, i = e - tt * ncols;
+                sv[tt * CB + i] = pv[x];
+            }
+        }
+        if ((int)threadIdx.x < n) {
+            sv[chunk * CB + threadIdx.x] = pg;
+            sv[chunk * CB + chunk + threadIdx.x] = pb;
+        }
+    };
+    issue(0, lo, min(chunk, hi - lo));
+    fetch(lo, min(chunk, hi - lo));
+    int stg = 0;
+    for (int base = lo; base < hi; base += chunk, stg ^= 1) {
+        const int n = min(chunk, hi - base);
+        park(stg, n);
+        const int nb = base + chunk;
+        __syncthreads();                                            // the other stage's readers are done
+        if (nb < hi) {
+            issue(stg ^ 1, nb, min(chunk, hi - nb));
+            fetch(nb, min(chunk, hi - nb));
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();                                            // this stage is complete for everybody
+        const float* sq = sm + stg * stage;
+        const float* sk = sq + chunk * DP;
+        const float* sv = sk + chunk * DP;
+        const float* sg = sv + chunk * CB;
+        const float* sb = sg + chunk;
+        float* sc = sm + stg * stage + chunk * (2 * DP + CB + 2);
+        // c = k . q of the chunk's tokens, eight lanes a token
+        // (every lane runs every round of the loop, so that the shuffles meet whole warps)
+        for (int t0 = 0; t0 < n; t0 += blockDim.x >> 3) {
+            const int tt = t0 + (threadIdx.x >> 3);
+            float c = 0.f;
+            if (tt < n)
+                for (int i = threadIdx.x & 7; i < DP; i += 8) c += sk[tt * DP + i] * sq[tt * DP + i];
+            c += __shfl_xor_sync(0xffffffffu, c, 1);
+            c += __shfl_xor_sync(0xffffffffu, c, 2);
+            c += __shfl_xor_sync(0xffffffffu, c, 4);
+            if (tt < n && (threadIdx.x & 7) == 0) sc[tt] = c;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int tt = 0; tt < n; ++tt) {
+            const float4* kt = reinterpret_cast<const float4*>(sk + tt * DP) + part;
+            const float4* qt = reinterpret_cast<const float4*>(sq + tt * DP) + part;
+            const float gt = sg[tt];
+            float kk[DPER];
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int i4 = 0; i4 < DPER / 4; ++i4) {
+                const float4 k4 = kt[i4 * PARTS], q4 = qt[i4 * PARTS];
+                kk[4 * i4] = k4.x; kk[4 * i4 + 1] = k4.y; kk[4 * i4 + 2] = k4.z; kk[4 * i4 + 3] = k4.w;
+                if (DELTA) {
+                    a0 += S[4 * i4] * k4.x;     a1 += S[4 * i4 + 1] * k4.y;
+                    a0 += S[4 * i4 + 2] * k4.z; a1 += S[4 * i4 + 3] * k4.w;
                 }
-                for (int off = parts >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-                u = sb[tt] * (u - dot);
+                b0 += S[4 * i4] * q4.x;     b1 += S[4 * i4 + 1] * q4.y;
+                b0 += S[4 * i4 + 2] * q4.z; b1 += S[4 * i4 + 3] * q4.w;
+            }
+            float a = a0 + a1, b = b0 + b1;
+            const float c = sc[tt];
+#pragma unroll
+            for (int off = PARTS >> 1; off > 0; off >>= 1) {
+                if (DELTA) a += __shfl_xor_sync(0xffffffffu, a, off);
+                b += __shfl_xor_sync(0xffffffffu, b, off);
+            }
+            float u = live ? sv[tt * CB + jl] : 0.f;
+            if (DELTA) u = sb[tt] * (u - gt * a);
+#pragma unroll
+            for (int i = 0; i < DPER; ++i) S[i] = S[i] * gt + kk[i] * u;
+            if (live && part == 0) o[((size_t)(base + tt) * H + h) * dv + j] = gt * b + u * c;
+        }
+    }
+    if (st) {
+#pragma unroll
+        for (int i4 = 0; i4 < DPER / 4; ++i4) {
+            const int r0 = 4 * (i4 * PARTS + part);
+            if (vec && r0 < d) {
+                *reinterpret_cast<float4*>(st + r0) = make_float4(S[4 * i4], S[4 * i4 + 1], S[4 * i4 + 2], S[4 * i4 + 3]);
             } else {
 #pragma unroll
-                for (int i = 0; i < DPER; ++i) S[i] *= gt;
+                for (int i = 0; i < 4; ++i)
+                    if (r0 + i < d) st[r0 + i] = S[4 * i4 + i];
             }
-            float out = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPER; ++i) {
-                if (d0 + i < d) {
-                    S[i] += kt[i] * u;
-                    out += S[i] * qt[i];
-                }
-            }
-            for (int off = parts >> 1; off > 0; off >>= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
-            if (live && part == 0) o[((size_t)(base + tt) * H + h) * dv + j] = out;
         }
     }
-    if (st && live) {
-#pragma unroll
-        for (int i = 0; i < DPER; ++i)
-            if (d0 + i < d) st[(size_t)(d0 + i) * dv + j] = S[i];
-    }
 }
+
+// For measurements: rows of S per thread (4, 8, 16 or 32) instead of the launcher's own choice; 0 gives it back.
+static int rg_scan_rows_override = 0;
+extern "C" void rg_state_scan_rows(int rows) { rg_scan_rows_override = rows; }
 
 extern "C" int rg_state_scan(const float* q, int q_ld, const float* k, int k_ld, const void* v, int v_dtype, int v_ld,
                              const float* decay, const float* g, const float* beta, float* state,
                              const int* cu_seqlens, const int* start_pos, const int* slots, float* o, int R, int H,
                              int Hqk, int d, int dv, void* stream) {
     if (R <= 0) return 0;
-    if (H < 1 || Hqk < 1 || H % Hqk || d < 1 || dv < 1 || d > 256 || dv > 1024 || (!decay && !g) || (beta && !g))
+    if (H < 1 || Hqk < 1 || H % Hqk || d < 1 || dv < 1 || d > 256 || (!decay && !g) || (beta && !g))
         return RG_ERR_UNSUPPORTED;
-    // rows of S per thread: 8 up to d = 64, then 16, then 32 (`parts` a power of two, at most 32 lanes wide;
-    // parts * columns at most 1024 threads)
+    // Rows of S per thread: 8 up to d = 64, then 16, then 32; `parts` (a power of two) threads share a column, and a
+    // block of at most SCAN_THREADS threads takes CB columns.  While that gives fewer blocks than SMs (a long prompt
+    // alone), threads take half as many rows each, down to 8 (measured, one prompt of 4,096 tokens, 16 heads of
+    // 128 x 128: 1.37 ms with 16 rows, 1.33 with 8, 1.55 with 4, where the shuffles outweigh the products).
     int dper = d <= 64 ? 8 : (d <= 128 ? 16 : 32);
-    int parts = 1;
-    while (parts * dper < d) parts <<= 1;
-    while (parts > 1 && (long long)parts * dv > 1024) { parts >>= 1; dper <<= 1; }
-    if (dper > 32 || parts > 32) return RG_ERR_UNSUPPORTED;
-    int threads = ((parts * dv + 31) / 32) * 32;
-    if (threads > 1024) return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(SCAN_CHUNK * (2 * d + dv) + 2 * SCAN_CHUNK) * sizeof(float);
-    if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
-    if (H > 65535) return RG_ERR_UNSUPPORTED;
+    auto shape = [&](int dp, int& parts, int& CB, int& col_blocks) {
+        parts = 1;
+        while (parts * dp < d) parts <<= 1;
+        CB = SCAN_THREADS / parts;
+        if (CB > dv) CB = dv;
+        col_blocks = (dv + CB - 1) / CB;
+    };
+    int parts, CB, col_blocks;
+    shape(dper, parts, CB, col_blocks);
+    if (rg_scan_rows_override > 0) {
+        dper = rg_scan_rows_override;
+        shape(dper, parts, CB, col_blocks);
+        if (parts > 32 || parts * dper > 256) return RG_ERR_UNSUPPORTED;
+    } else
+    while ((long long)R * H * col_blocks < 148 && dper > 8) {
+        int p2, c2, b2;
+        shape(dper / 2, p2, c2, b2);
+        if (p2 > 32) break;
+        dper /= 2; parts = p2; CB = c2; col_blocks = b2;
+    }
+    const int threads = ((parts * CB + 31) / 32) * 32;
+    const int DP = parts * dper;
+    int chunk = DP > 128 ? 8 : 16;
+    if (chunk > 4 * parts) chunk = 4 * parts;                      // what a thread prefetches of v stays in 4 registers
+    if (chunk * CB > SCAN_MAX_PREFETCH * threads) return RG_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)2 * chunk * (2 * DP + CB + 3) * sizeof(float);
+    if (smem > 48 * 1024 || H > 65535 || col_blocks > 65535) return RG_ERR_UNSUPPORTED;
+    // 16-byte copies and state accesses where every row starts on a 16-byte boundary
+    const int vec = d % 4 == 0 && q_ld % 4 == 0 && k_ld % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 &&
+                    ((uintptr_t)state & 15) == 0;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(R, H);
-#define SM_SCAN(DP, V) return rg_launch(state_scan_kernel<DP, V>, grid, dim3(threads), smem, s, 1, q, q_ld, k, k_ld, \
-        (const V*)v, v_ld, decay, g, beta, state, cu_seqlens, start_pos, slots, o, H, Hqk, d, dv, parts)
-    if (v_dtype == RG_DTYPE_F32) {
-        if (dper == 8) SM_SCAN(8, float);
-        if (dper == 16) SM_SCAN(16, float);
-        SM_SCAN(32, float);
-    }
-    if (v_dtype == RG_DTYPE_BF16) {
-        if (dper == 8) SM_SCAN(8, bf16);
-        if (dper == 16) SM_SCAN(16, bf16);
-        SM_SCAN(32, bf16);
-    }
+    dim3 grid(R, H, col_blocks);
+#define SM_SCAN(DP_, PA_, DE_, V) return rg_launch(state_scan_kernel<DP_, PA_, DE_, V>, grid, dim3(threads), smem, s, 1, \
+        q, q_ld, k, k_ld, (const V*)v, v_ld, decay, g, beta, state, cu_seqlens, start_pos, slots, o, H, Hqk, d, dv, CB, \
+        chunk, vec)
+#define SM_SCAN_RULE(DP_, PA_, V) { if (beta) SM_SCAN(DP_, PA_, true, V); SM_SCAN(DP_, PA_, false, V); }
+#define SM_SCAN_PARTS(DP_, V) switch (parts) { \
+        case 1: SM_SCAN_RULE(DP_, 1, V) case 2: SM_SCAN_RULE(DP_, 2, V) case 4: SM_SCAN_RULE(DP_, 4, V) \
+        case 8: SM_SCAN_RULE(DP_, 8, V) case 16: if (DP_ <= 16) SM_SCAN_RULE(DP_ <= 16 ? DP_ : 16, 16, V) break; \
+        case 32: if (DP_ <= 8) SM_SCAN_RULE(DP_ <= 8 ? DP_ : 8, 32, V) break; default: break; } \
+        return RG_ERR_UNSUPPORTED;
+#define SM_SCAN_ROWS(V) switch (dper) { case 4: SM_SCAN_PARTS(4, V) case 8: SM_SCAN_PARTS(8, V) \
+        case 16: SM_SCAN_PARTS(16, V) case 32: SM_SCAN_PARTS(32, V) default: return RG_ERR_UNSUPPORTED; }
+    if (v_dtype == RG_DTYPE_F32) SM_SCAN_ROWS(float)
+    if (v_dtype == RG_DTYPE_BF16) SM_SCAN_ROWS(bf16)
     return RG_ERR_UNSUPPORTED;
+#undef SM_SCAN_ROWS
+#undef SM_SCAN_PARTS
+#undef SM_SCAN_RULE
 #undef SM_SCAN
 }
 

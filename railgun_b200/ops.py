@@ -911,7 +911,7 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
                decay: torch.Tensor | None = None, g: torch.Tensor | None = None,
                beta: torch.Tensor | None = None) -> torch.Tensor:
     """A matrix S [d, dv] per head carried along each request's tokens, 32-bit, from the request's slot of ``state``
-    [slots, H, d, dv] (zeros at position 0) and left there.  With ``decay`` [H]: S <- decay_h S + k v^T; with ``g``
+    [slots, H, dv, d] (S transposed; zeros at position 0) and left there.  With ``decay`` [H]: S <- decay_h S + k v^T; with ``g``
     and ``beta`` [T, H]: S <- g S, u = beta (v - S^T k), S <- S + k u^T.  Either way o = S^T q after the update.
     ``q``, ``k``: float32 [T, Hqk * d] views (head h reads head h / (H / Hqk)); ``v``: [T, H * dv] view, float32 or
     bfloat16.
@@ -923,7 +923,7 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
     T = q.shape[0]
     Hqk = q.shape[1] // d
     if q.shape[1] != Hqk * d or k.shape != q.shape or v.shape != (T, H * dv) or Hqk < 1 or H % Hqk \
-            or tuple(state.shape[1:]) != (H, d, dv):
+            or tuple(state.shape[1:]) != (H, dv, d):
         raise KernelError(f"state_scan: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, state "
                           f"{tuple(state.shape)} do not match {H} heads of {d} x {dv}")
     for t, name, n in ((decay, "decay", H), (g, "g", T * H), (beta, "beta", T * H)):
@@ -940,6 +940,12 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
         _ptr(beta), _ptr(state), _ptr(batch.cu_seqlens), _ptr(batch.start_pos), _ptr(batch.state_slots), _ptr(o),
         c_int(batch.num_requests), c_int(H), c_int(Hqk), c_int(d), c_int(dv), _stream()), "state_scan")
     return o
+
+
+def state_scan_rows(rows: int) -> None:
+    """For measurements: make ``state_scan`` give every thread ``rows`` rows of S (4, 8, 16 or 32) instead of the
+    launcher's own choice; 0 gives the choice back."""
+    _fn("state_mixers", "rg_state_scan_rows")(c_int(rows))
 
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight, eps: float, out_dtype) -> torch.Tensor:
@@ -1313,18 +1319,19 @@ def _check_paged(q, kv_cache, block_table, nkv, d):
 
 
 def prefill_attention(q, q_stride: int, out, kv_cache, block_table, tiles, positions, nh: int, nkv: int, d: int,
-                      window: int, scale: float) -> None:
+                      window: int, scale: float, keep_first: int = 0) -> None:
     """Flash-style attention for requests that bring several tokens: ``tiles``
     [n, 3] = (first row, rows <= 64, request index).  Writes the tiles' rows of
-    ``out`` [T, nh*d]."""
+    ``out`` [T, nh*d].  ``keep_first``: with a window, the first positions of a
+    request that every later query still sees."""
     page_size = _check_paged(q, kv_cache, block_table, nkv, d)
     _check(tiles, "tiles", torch.int32)
     _check(positions, "positions", torch.int32)
     _check(out, "out", q.dtype)
-    _ok(_fn("attention_mma", "rg_prefill_attention")(
+    _ok(_fn("attention_mma", "rg_prefill_attention_keep")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(tiles), c_int(tiles.shape[0]), _ptr(positions), c_int(nh), c_int(nkv), c_int(d), c_int(page_size),
-        c_int(window or 0), c_float(scale), _stream()), "prefill_attention")
+        c_int(window or 0), c_int(keep_first if window else 0), c_float(scale), _stream()), "prefill_attention")
 
 
 def decode_splits(n_tokens: int, kv_tiles: int, max_context: int) -> int:
@@ -1342,7 +1349,7 @@ _decode_counters: dict = {}
 
 def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_tokens: int, req_of_token, positions,
                      nh: int, nkv: int, d: int, window: int, scale: float, num_splits: int,
-                     scratch=None, fused_reduce=None, cluster: bool = False) -> None:
+                     scratch=None, fused_reduce=None, cluster: bool = False, keep_first: int = 0) -> None:
     """Split attention for single tokens: token rows ``rows`` (None: rows
     0..n_tokens-1) each attend their request's context.  Partial results go
     through scratch memory (allocated here unless given) and are reduced into
@@ -1353,7 +1360,9 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
     splits of a (token, head tile) are one thread-block cluster and add their
     partial results through distributed shared memory; the fastest way for the
     kernel alone, not inside a decode step (see attention_mma.cu), so the
-    engine leaves it off.  Every way adds the splits in split order."""
+    engine leaves it off.  Every way adds the splits in split order.
+    ``keep_first``: with a window, the first positions of a request that every
+    later query still sees (not with ``cluster``)."""
     if fused_reduce is None:
         fused_reduce = num_splits == 1
     page_size = _check_paged(q, kv_cache, block_table, nkv, d)
@@ -1363,6 +1372,8 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
     if rows is not None:
         _check(rows, "rows", torch.int32)
     if cluster:
+        if keep_first and window:
+            raise KernelError("decode_attention: the cluster form does not keep first tokens")
         if not 2 <= num_splits <= 8:
             raise KernelError("decode_attention: a cluster takes 2 to 8 splits")
         _ok(_fn("attention_mma", "rg_decode_attention_cluster")(
@@ -1386,11 +1397,11 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
             counters = _decode_counters[q.device] = torch.zeros(max(need, 4096), dtype=torch.int32, device=q.device)
     else:
         _COUNTER.value += 1                  # the launcher runs two kernels: partial results, then the reduction
-    _ok(_fn("attention_mma", "rg_decode_attention")(
+    _ok(_fn("attention_mma", "rg_decode_attention_keep")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(rows), c_int(n_tokens), _ptr(req_of_token), _ptr(positions), _ptr(part_o), _ptr(part_ml),
-        _ptr(counters), c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0), c_float(scale),
-        c_int(num_splits), _stream()), "decode_attention")
+        _ptr(counters), c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0),
+        c_int(keep_first if window else 0), c_float(scale), c_int(num_splits), _stream()), "decode_attention")
 
 
 _tc_err: dict = {}

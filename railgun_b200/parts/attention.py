@@ -244,10 +244,11 @@ class NormedAttention(Mixer):
 
     def attend(self, q, batch, cache):
         """bfloat16 runs on the tensor cores (requests with several tokens through the flash-style kernel, single
-        tokens through the split kernel); the 32-bit path runs the general kernel."""
+        tokens through the split kernel; both know the window and the kept first tokens); the 32-bit path runs the
+        general kernel."""
         H, G, D = self.H, self.G, self.D
         table = batch.block_table[cache.group]
-        if q.dtype != torch.bfloat16 or self.keep_first:
+        if q.dtype != torch.bfloat16:
             return ops.paged_attention_general(q, q.shape[1], cache.kv, table, batch.req_of_token, batch.positions,
                                                H, G, D, self.window, 1.0, self.keep_first)
         out = torch.empty((q.shape[0], H * D), dtype=q.dtype, device=q.device)
@@ -257,12 +258,12 @@ class NormedAttention(Mixer):
             reach = min(reach, self.window + self.keep_first)
         if batch.num_prefill_tiles:
             ops.prefill_attention(q, q.shape[1], out, cache.kv, table, batch.prefill_tiles, batch.positions,
-                                  H, G, D, self.window, 1.0)
+                                  H, G, D, self.window, 1.0, self.keep_first)
         n = batch.num_tokens if batch.decode_only else batch.num_decode_rows
         if n:
             ops.decode_attention(q, q.shape[1], out, cache.kv, table, None if batch.decode_only else batch.decode_rows,
                                  n, batch.req_of_token, batch.positions, H, G, D, self.window, 1.0,
-                                 ops.decode_splits(n, kv_tiles, reach))
+                                 ops.decode_splits(n, kv_tiles, reach), keep_first=self.keep_first)
         return out
 
 

@@ -21,8 +21,9 @@ g = exp(-exp(A_log) softplus(W_a h + dt_bias)) per head:
 convolution per channel over the request's tokens, instead of h.
 
 Between steps a request keeps, in its state slot and in 32-bit: S of every
-head, and the last taps - 1 inputs of every convolution.  Everything from the
-projections' outputs to the rounding before the output product is 32-bit.
+head (transposed, [dv, d]), and the last taps - 1 inputs of every
+convolution.  Everything from the projections' outputs to the rounding
+before the output product is 32-bit.
 """
 from __future__ import annotations
 
@@ -54,7 +55,7 @@ class Retention(Mixer):
 
     @classmethod
     def cache_need(cls, p):
-        return StateNeed((int(p["num_heads"]), int(p["head_dim"]), int(p["v_dim"])), "float32")
+        return StateNeed((int(p["num_heads"]), int(p["v_dim"]), int(p["head_dim"])), "float32")     # S transposed
 
     def __init__(self, p, prefix, env, tensors):
         super().__init__(p, prefix, env, tensors)
@@ -106,7 +107,7 @@ class GatedDelta(Mixer):
     @classmethod
     def cache_need(cls, p):
         H, G, d, dv, K = p["num_heads"], p["num_qk_heads"], p["head_dim"], p["v_dim"], p["taps"]
-        need = [StateNeed((int(H), int(d), int(dv)), "float32")]
+        need = [StateNeed((int(H), int(dv), int(d)), "float32")]            # S transposed
         if K > 1:
             need.append(StateNeed((int(K) - 1, 2 * G * d + H * dv), "float32"))
         return tuple(need)

@@ -221,9 +221,10 @@ def moe_ff(h, w, p, mlp, margins=None):
 def layer(x, w, cfg, i, margins=None):
     L = cfg["layers"][i]
     p = f"l{i}."
-    eps, groups = cfg["norm"]["eps"], cfg["norm"]["groups"]
+    eps, groups = cfg["norm"]["eps"], cfg["norm"].get("groups", 1)
     h = group_norm(x, w[p + "norm1"], groups, eps)
-    h = h + causal_conv(h, w[p + "canon1"])
+    if (cfg.get("canon") or {}).get("taps"):
+        h = h + causal_conv(h, w[p + "canon1"])
     y = MIXERS[L["type"]](h, w, p + "mix.", L["mixer"], eps)
     mlp = L.get("mlp")
     if mlp is not None:
@@ -234,11 +235,11 @@ def layer(x, w, cfg, i, margins=None):
 
 def forward(tokens, w, cfg, keep_layers=False, margins=None):
     """Logits [T, vocab] of one sequence (and the residual stream after every layer, if asked)."""
-    x = w["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
+    x = w["embed"][np.asarray(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     after = []
     for i in range(len(cfg["layers"])):
         x = layer(x, w, cfg, i, margins)
         if keep_layers:
             after.append(x.copy())
-    logits = group_norm(x, w["final.norm"], cfg["norm"]["groups"], cfg["norm"]["eps"]) @ w["head"].T
+    logits = group_norm(x, w["final.norm"], cfg["norm"].get("groups", 1), cfg["norm"]["eps"]) @ w["head"].T
     return (logits, np.stack(after)) if keep_layers else logits
