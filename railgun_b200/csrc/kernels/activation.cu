@@ -187,12 +187,39 @@ __global__ void gated_activation_kernel(const A* __restrict__ gu, A* __restrict_
     out[idx] = from_f32<A>(gated_act(to_f32(gu[t * 2 * I + i]), to_f32(gu[t * 2 * I + I + i]), kind, limit));
 }
 
+// The same for bfloat16 rows whose halves start on 16-byte boundaries: eight numbers per thread.
+__global__ void gated_activation8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I8, int kind,
+                                         float limit, size_t total8) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const size_t t = idx / I8, i = idx - t * I8;
+    const uint4 g4 = reinterpret_cast<const uint4*>(gu)[t * 2 * I8 + i];
+    const uint4 u4 = reinterpret_cast<const uint4*>(gu)[t * 2 * I8 + I8 + i];
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+        o2[j] = __floats2bfloat162_rn(gated_act(g.x, u.x, kind, limit), gated_act(g.y, u.y, kind, limit));
+    }
+    reinterpret_cast<uint4*>(out)[idx] = o4;
+}
+
 extern "C" int rg_gated_activation(const void* gu, void* out, int dtype, int T, int I, int kind, float limit,
                                    void* stream) {
     if (T <= 0 || I <= 0) return 0;
     if (kind < 0 || kind > 2) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)T * I;
+    if (dtype == RG_DTYPE_BF16 && I % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        const size_t total8 = total / 8;
+        return rg_launch(gated_activation8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, s, 1,
+                         (const bf16*)gu, (bf16*)out, I / 8, kind, limit, total8);
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(gated_activation_kernel<bf16>, dim3(blocks), dim3(256), 0, s, 1, (const bf16*)gu, (bf16*)out, I,

@@ -53,6 +53,65 @@ __global__ void causal_conv_kernel(const A* __restrict__ x, int ld, int x_off, c
     out[(size_t)t * out_ld + c] = from_f32<O>(acc);
 }
 
+// The same for bfloat16 inputs with eight channels per thread (16-byte loads), where rows and offsets allow it.
+template <typename O>
+__global__ void causal_conv8_kernel(const bf16* __restrict__ x, int ld, int x_off, const float* __restrict__ taps,
+                                    const float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                                    const int* __restrict__ req_of_token, const int* __restrict__ start_pos,
+                                    const int* __restrict__ slots, O* __restrict__ out, int out_ld, int C, int K,
+                                    int residual, int act) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) return;
+    const int r = req_of_token[t];
+    const int i = t - cu_seqlens[r];
+    const int slot = slots[r];
+    const bool has_past = slot >= 0 && start_pos[r] > 0;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float cur[8];
+    for (int j = 0; j < K; ++j) {
+        const int idx = i - (K - 1) + j;
+        float v[8];
+        if (idx >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t - (K - 1) + j) * ld + x_off + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        } else if (has_past) {
+            const float4* p = reinterpret_cast<const float4*>(state + ((size_t)slot * (K - 1) + (K - 1 + idx)) * C + c);
+            const float4 a = p[0], b = p[1];
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += taps[(size_t)(c + e) * K + j] * v[e];
+        if (j == K - 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) cur[e] = v[e];
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        if (act == 1) acc[e] = acc[e] * sm_sigmoid(acc[e]);
+        if (residual) acc[e] += cur[e];
+    }
+    O* o = out + (size_t)t * out_ld + c;
+    if (sizeof(O) == 2) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        *reinterpret_cast<uint4*>(o) = pk;
+    } else {
+        reinterpret_cast<float4*>(o)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        reinterpret_cast<float4*>(o)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
+
 // One thread per (request, channel): rows in ascending order, each read from a later row (or from the step's
 // tokens) before that row is written.
 template <typename A>
@@ -87,6 +146,19 @@ extern "C" int rg_causal_conv(const void* x, int x_dtype, int ld, int x_off, con
     if (T <= 0 || C <= 0) return 0;
     if (K < 1 || (K > 1 && !state) || act < 0 || act > 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    const int out_align = out_dtype == RG_DTYPE_BF16 ? 8 : 4;
+    if (x_dtype == RG_DTYPE_BF16 && C % 8 == 0 && x_off % 8 == 0 && ld % 8 == 0 && out_ld % out_align == 0 &&
+        ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0) {
+        const int th = C / 8 >= 128 ? 128 : 64;
+        dim3 g8(T, (C / 8 + th - 1) / th);
+        if (g8.y > 65535) return RG_ERR_UNSUPPORTED;
+        if (out_dtype == RG_DTYPE_BF16)
+            return rg_launch(causal_conv8_kernel<bf16>, g8, dim3(th), 0, s, 1, (const bf16*)x, ld, x_off, taps, state,
+                             cu_seqlens, req_of_token, start_pos, slots, (bf16*)out, out_ld, C, K, residual, act);
+        if (out_dtype == RG_DTYPE_F32)
+            return rg_launch(causal_conv8_kernel<float>, g8, dim3(th), 0, s, 1, (const bf16*)x, ld, x_off, taps, state,
+                             cu_seqlens, req_of_token, start_pos, slots, (float*)out, out_ld, C, K, residual, act);
+    }
     const int threads = C >= 256 ? 256 : 128;
     dim3 grid(T, (C + threads - 1) / threads);
     if (grid.y > 65535) return RG_ERR_UNSUPPORTED;

@@ -70,6 +70,22 @@ def test_group_norm_alone(T, W, groups, dtype):
     assert rel(c, P.group_norm(total, w1, groups, 1e-5)[[T - 1, 0]]) < 2e-6
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("I", [24, 12, 7, 512])
+def test_gated_activations_alone(I, dtype):
+    """gate | up rows through the three gated activations, with numbers on both sides of the clamps."""
+    from railgun_b200 import ops
+    rng = np.random.default_rng(I)
+    gu = torch.tensor(rng.normal(size=(37, 2 * I)) * 2.0, dtype=TORCH[dtype])
+    g, u = gu[:, :I].double().numpy(), gu[:, I:].double().numpy()
+    silu = lambda z: z / (1.0 + np.exp(-z))
+    want = {"silu": silu(g) * u, "gelu_tanh": P.gelu_tanh(g) * u,
+            "clamped_swish": np.minimum(g, 1.25) / (1.0 + np.exp(-1.702 * np.minimum(g, 1.25))) * (np.clip(u, -1.25, 1.25) + 1.0)}
+    for kind, ref in want.items():
+        got = ops.gated_activation(gu.to(DEV), kind, 1.25)
+        assert rel(got, ref) < (2e-6 if dtype == "float32" else 6e-3), kind
+
+
 # ---- the short convolution and its state ---------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES)
