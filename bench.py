@@ -1078,7 +1078,7 @@ def run_kernels(args):
             by, by2 = T * W * (8 + 2 + 4), T * W * (8 + 2 + 2)
             out(f"norm in 4 groups, two outputs W{W} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
                 add_rmsnorm_us=round(us2, 2), add_rmsnorm_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))
-            taps = torch.randn(W, K, device=dev) * 0.3
+            taps = torch.randn(K, W, device=dev) * 0.3
             cstate = [torch.randn(R_, K - 1, W, device=dev) for _ in range(L)]
             us = timed(lambda: [(ops.causal_conv(y, 0, taps, c, batch, torch.bfloat16, residual=True),
                                  ops.conv_state_update(y, 0, c, batch)) for y, c in zip(ys, cstate)])

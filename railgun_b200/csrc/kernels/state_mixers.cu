@@ -23,7 +23,8 @@
 __device__ __forceinline__ float sm_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float sm_softplus(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f); }
 
-// x: rows ld apart, channel c at column x_off + c.  state [slots, K - 1, C] float, oldest input first.
+// x: rows ld apart, channel c at column x_off + c.  taps [K, C] float (tap-major, so that neighbouring channels
+// are neighbouring numbers; row K - 1 is the current token's).  state [slots, K - 1, C] float, oldest input first.
 // out: rows out_ld apart (type O).  residual: out = x + conv(x); act 1: silu of the convolution.
 template <typename A, typename O>
 __global__ void causal_conv_kernel(const A* __restrict__ x, int ld, int x_off, const float* __restrict__ taps,
@@ -46,7 +47,7 @@ __global__ void causal_conv_kernel(const A* __restrict__ x, int ld, int x_off, c
         float v;
         if (idx >= 0) v = to_f32(x[(size_t)(t - (K - 1) + j) * ld + x_off + c]);
         else v = has_past ? state[((size_t)slot * (K - 1) + (K - 1 + idx)) * C + c] : 0.f;
-        acc += taps[(size_t)c * K + j] * v;
+        acc += taps[(size_t)j * C + c] * v;
     }
     if (act == 1) acc = acc * sm_sigmoid(acc);
     if (residual) acc += to_f32(x[(size_t)t * ld + x_off + c]);
@@ -87,8 +88,10 @@ __global__ void causal_conv8_kernel(const bf16* __restrict__ x, int ld, int x_of
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] = 0.f;
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += taps[(size_t)(c + e) * K + j] * v[e];
+        const float4 w0 = *reinterpret_cast<const float4*>(taps + (size_t)j * C + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(taps + (size_t)j * C + c + 4);
+        acc[0] += w0.x * v[0]; acc[1] += w0.y * v[1]; acc[2] += w0.z * v[2]; acc[3] += w0.w * v[3];
+        acc[4] += w1.x * v[4]; acc[5] += w1.y * v[5]; acc[6] += w1.z * v[6]; acc[7] += w1.w * v[7];
         if (j == K - 1) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) cur[e] = v[e];
@@ -148,7 +151,8 @@ extern "C" int rg_causal_conv(const void* x, int x_dtype, int ld, int x_off, con
     cudaStream_t s = (cudaStream_t)stream;
     const int out_align = out_dtype == RG_DTYPE_BF16 ? 8 : 4;
     if (x_dtype == RG_DTYPE_BF16 && C % 8 == 0 && x_off % 8 == 0 && ld % 8 == 0 && out_ld % out_align == 0 &&
-        ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0) {
+        ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0 &&
+        ((uintptr_t)taps & 15) == 0) {
         const int th = C / 8 >= 128 ? 128 : 64;
         dim3 g8(T, (C / 8 + th - 1) / th);
         if (g8.y > 65535) return RG_ERR_UNSUPPORTED;

@@ -825,14 +825,15 @@ def recurrent_scan(proj: torch.Tensor, y_off: int, x_off: int, yb, xb, u: torch.
 
 def causal_conv(x: torch.Tensor, x_off: int, taps: torch.Tensor, state, batch, out_dtype, residual: bool = False,
                 silu: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
-    """[T, C]: per channel the causal convolution of x[:, x_off:x_off + C] with ``taps`` [C, K] (last column: the
+    """[T, C]: per channel the causal convolution of x[:, x_off:x_off + C] with ``taps`` [K, C] (tap-major: what the
+    tensor files hold as [C, K], transposed once at load; last row: the
     current token's) along each request's tokens, continued from the K - 1 inputs in the request's state slot
     (``state`` [slots, K - 1, C] float32; None when K = 1) unless the request starts at position 0.  ``silu``:
     the activation on the convolution; ``residual``: x is added.  32-bit arithmetic, one rounding into
     ``out_dtype``.  The state is not changed (``conv_state_update`` does that, afterwards)."""
     _check_rows(x, "x")
     _check(taps, "taps", torch.float32)
-    C, K = taps.shape
+    K, C = taps.shape
     T = x.shape[0]
     if x.shape[1] < x_off + C:
         raise KernelError(f"causal_conv: {C} channels from column {x_off} of rows of {x.shape[1]}")

@@ -126,7 +126,7 @@ class GatedDelta(Mixer):
         self.w_in = torch.cat([tensors.get(b + n, env.dtype) for n in ("q", "k", "v", "g")], dim=0).contiguous()
         self.w_ba = torch.cat([tensors.get(b + n, env.dtype) for n in ("b", "a")], dim=0).contiguous()
         tensors.drop(b + "q", b + "k", b + "v", b + "g", b + "b", b + "a")
-        self.taps = torch.cat([f32("q.conv"), f32("k.conv"), f32("v.conv")], dim=0).contiguous()
+        self.taps = torch.cat([f32("q.conv"), f32("k.conv"), f32("v.conv")], dim=0).t().contiguous()    # [taps, channels]
         self.A_log, self.dt_bias, self.norm = f32("A_log"), f32("dt_bias"), f32("norm")
         self.w_o = tensors.get(b + "o", env.dtype)
 
@@ -175,7 +175,7 @@ class InputConv(Mixer):
         self.inner = MIXERS.get(inner.kind)(inner.params, prefix, env, tensors)
         self.inner_composite = self._inner_needs(p)[1]
         self.K = int(p["taps"])
-        self.taps = tensors.get(prefix + p["name"], torch.float32).contiguous()
+        self.taps = tensors.get(prefix + p["name"], torch.float32).t().contiguous()                # [taps, channels]
         self.graph_safe = getattr(self.inner, "graph_safe", True)
 
     def forward(self, x, batch, cache, writes=True):

@@ -108,10 +108,10 @@ def test_convolution_continues_from_the_state(C_, K, dtype):
                           P.causal_conv(np.concatenate([past(1), xin[5:12]]), taps)[K - 1:],
                           P.causal_conv(np.concatenate([past(3), xin[12:]]), taps)[K - 1:]])
     tol = 2e-6 if dtype == "float32" else 8e-3
-    plain = ops.causal_conv(dev(x), 8, dev(taps, torch.float32), st, batch, torch.float32)
+    plain = ops.causal_conv(dev(x), 8, dev(np.ascontiguousarray(taps.T), torch.float32), st, batch, torch.float32)
     assert rel(plain, ref) < 2e-6
-    assert rel(ops.causal_conv(dev(x), 8, dev(taps, torch.float32), st, batch, TORCH[dtype], residual=True), ref + xin) < tol
-    assert rel(ops.causal_conv(dev(x), 8, dev(taps, torch.float32), st, batch, torch.float32, silu=True), P.silu(ref)) < 2e-6
+    assert rel(ops.causal_conv(dev(x), 8, dev(np.ascontiguousarray(taps.T), torch.float32), st, batch, TORCH[dtype], residual=True), ref + xin) < tol
+    assert rel(ops.causal_conv(dev(x), 8, dev(np.ascontiguousarray(taps.T), torch.float32), st, batch, torch.float32, silu=True), P.silu(ref)) < 2e-6
     if K > 1:
         assert torch.equal(st.cpu(), state)                                   # reading changes nothing
         ops.conv_state_update(dev(x), 8, st, batch)
