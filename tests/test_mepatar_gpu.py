@@ -50,7 +50,8 @@ def step_batch(lengths, starts, slots):
 # ---- the norm in groups ------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,W,groups", [(3, 24, 1), (5, 64, 2), (9, 48, 3), (300, 256, 4), (2, 40, 5), (70, 1536, 6)])
+@pytest.mark.parametrize("T,W,groups", [(3, 24, 1), (5, 64, 2), (9, 48, 3), (300, 256, 4), (2, 40, 5), (70, 1536, 6),
+                                          (4, 30, 3), (6, 42, 7), (33, 2050, 1)])
 def test_group_norm_alone(T, W, groups, dtype):
     """The residual takes the pending rows in 32-bit; two norms read the same sum; one loud part stays alone."""
     from railgun_b200 import ops
