@@ -319,7 +319,7 @@ state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict
     extern __shared__ __align__(16) float sm[];
     constexpr int parts = PARTS;
     constexpr int DP = PARTS * DPER;                 // padded length of a q or k row
-    const int stage = chunk * (2 * DP + CB + 3);     // floats of one stage: q, k [chunk][DP], v [chunk][CB], g, beta, c
+    const int stage = chunk * (2 * DP + CB + 4);     // floats of one stage: q, k [chunk][DP], v [chunk][CB], (g, beta, c, -) [chunk]
     pdl_wait();
     pdl_trigger();
     const int r = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * CB;
@@ -356,12 +356,32 @@ state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict
         }
     }
     float pv[SCAN_MAX_PREFETCH], pg = 0.f, pb = 0.f;
+    // this thread's places in a chunk's tile of v (the same in every chunk), and in the rows of q and k
+    int v_tt[SCAN_MAX_PREFETCH], v_i[SCAN_MAX_PREFETCH];
+#pragma unroll
+    for (int x = 0; x < SCAN_MAX_PREFETCH; ++x) {
+        const int e = threadIdx.x + x * blockDim.x;
+        v_tt[x] = e < chunk * ncols ? e / ncols : chunk;
+        v_i[x] = e - v_tt[x] * ncols;
+    }
+    const V* vh = v + (size_t)h * dv + j0;
+    const float* qh = q + (size_t)hq * d;
+    const float* kh = k + (size_t)hq * d;
+    const int d4 = d >> 2;
+    const bool by_rows = vec && d4 <= (int)blockDim.x;               // whole rows per pass: no division in the loop
+    const int rpp = by_rows ? blockDim.x / d4 : 1, row_t = threadIdx.x / (by_rows ? d4 : 1),
+              row_i = by_rows ? (threadIdx.x - row_t * d4) * 4 : 0;
     // q and k of `n` tokens from `base` on into stage `stg`, asynchronously
     auto issue = [&](int stg, int base, int n) {
         float* sq = sm + stg * stage;
         float* sk = sq + chunk * DP;
-        if (vec) {
-            const int d4 = d >> 2;
+        if (by_rows) {
+            if (row_t < rpp)
+                for (int tt = row_t; tt < n; tt += rpp) {
+                    scan_cp_async16(sq + tt * DP + row_i, qh + (size_t)(base + tt) * q_ld + row_i);
+                    scan_cp_async16(sk + tt * DP + row_i, kh + (size_t)(base + tt) * k_ld + row_i);
+                }
+        } else if (vec) {
             for (int e = threadIdx.x; e < n * d4; e += blockDim.x) {
                 const int tt = e / d4, i = (e - tt * d4) * 4;
                 scan_cp_async16(sq + tt * DP + i, q + (size_t)(base + tt) * q_ld + (size_t)hq * d + i);
@@ -379,13 +399,8 @@ state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict
     // v, g and beta of those tokens into registers; `park` leaves them in the stage
     auto fetch = [&](int base, int n) {
 #pragma unroll
-        for (int x = 0; x < SCAN_MAX_PREFETCH; ++x) {
-            const int e = threadIdx.x + x * blockDim.x;
-            if (e < n * ncols) {
-                const int tt = e / ncols, i = e - tt * ncols;
-                pv[x] = to_f32(v[(size_t)(base + tt) * v_ld + (size_t)h * dv + j0 + i]);
-            }
-        }
+        for (int x = 0; x < SCAN_MAX_PREFETCH; ++x)
+            if (v_tt[x] < n) pv[x] = to_f32(vh[(size_t)(base + v_tt[x]) * v_ld + v_i[x]]);
         if ((int)threadIdx.x < n) {
             pg = g ? g[(size_t)(base + threadIdx.x) * H + h] : fixed;
             pb = beta ? beta[(size_t)(base + threadIdx.x) * H + h] : 0.f;
@@ -394,18 +409,15 @@ state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict
     auto park = [&](int stg, int n) {
         float* sv = sm + stg * stage + 2 * chunk * DP;
 #pragma unroll
-        for (int x = 0; x < SCAN_MAX_PREFETCH; ++x) {
-            const int e = threadIdx.x + x * blockDim.x;
-            if (e < n * ncols) {
-                const int tt = e / ncols, i = e - tt * ncols;
-                sv[tt * CB + i] = pv[x];
-            }
-        }
+        for (int x = 0; x < SCAN_MAX_PREFETCH; ++x)
+            if (v_tt[x] < n) sv[v_tt[x] * CB + v_i[x]] = pv[x];
         if ((int)threadIdx.x < n) {
-            sv[chunk * CB + threadIdx.x] = pg;
-            sv[chunk * CB + chunk + threadIdx.x] = pb;
+            sv[chunk * CB + 4 * threadIdx.x] = pg;
+            sv[chunk * CB + 4 * threadIdx.x + 1] = pb;
         }
     };
+    float* op = o + ((size_t)lo * H + h) * dv + (live ? j : 0);
+    const size_t ostep = (size_t)H * dv;
     issue(0, lo, min(chunk, hi - lo));
     fetch(lo, min(chunk, hi - lo));
     int stg = 0;
@@ -425,27 +437,32 @@ state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict
         const float* sq = sm + stg * stage;
         const float* sk = sq + chunk * DP;
         const float* sv = sk + chunk * DP;
-        const float* sg = sv + chunk * CB;
-        const float* sb = sg + chunk;
-        float* sc = sm + stg * stage + chunk * (2 * DP + CB + 2);
+        float* sgbc = sm + stg * stage + chunk * (2 * DP + CB);      // (g, beta, c, -) of every token
         // c = k . q of the chunk's tokens, eight lanes a token
         // (every lane runs every round of the loop, so that the shuffles meet whole warps)
         for (int t0 = 0; t0 < n; t0 += blockDim.x >> 3) {
             const int tt = t0 + (threadIdx.x >> 3);
             float c = 0.f;
-            if (tt < n)
-                for (int i = threadIdx.x & 7; i < DP; i += 8) c += sk[tt * DP + i] * sq[tt * DP + i];
+            if (tt < n) {
+                const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DP);
+                const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DP);
+                for (int i = threadIdx.x & 7; i < DP / 4; i += 8) {
+                    const float4 a = k4[i], b = q4[i];
+                    c += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+                }
+            }
             c += __shfl_xor_sync(0xffffffffu, c, 1);
             c += __shfl_xor_sync(0xffffffffu, c, 2);
             c += __shfl_xor_sync(0xffffffffu, c, 4);
-            if (tt < n && (threadIdx.x & 7) == 0) sc[tt] = c;
+            if (tt < n && (threadIdx.x & 7) == 0) sgbc[4 * tt + 2] = c;
         }
         __syncthreads();
 #pragma unroll 2
         for (int tt = 0; tt < n; ++tt) {
             const float4* kt = reinterpret_cast<const float4*>(sk + tt * DP) + part;
             const float4* qt = reinterpret_cast<const float4*>(sq + tt * DP) + part;
-            const float gt = sg[tt];
+            const float4 gbc = *reinterpret_cast<const float4*>(sgbc + 4 * tt);
+            const float gt = gbc.x;
             float kk[DPER];
             float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
@@ -460,17 +477,18 @@ state_scan_kernel(const float* __restrict__ q, int q_ld, const float* __restrict
                 b0 += S[4 * i4 + 2] * q4.z; b1 += S[4 * i4 + 3] * q4.w;
             }
             float a = a0 + a1, b = b0 + b1;
-            const float c = sc[tt];
+            const float c = gbc.z;
 #pragma unroll
             for (int off = PARTS >> 1; off > 0; off >>= 1) {
                 if (DELTA) a += __shfl_xor_sync(0xffffffffu, a, off);
                 b += __shfl_xor_sync(0xffffffffu, b, off);
             }
             float u = live ? sv[tt * CB + jl] : 0.f;
-            if (DELTA) u = sb[tt] * (u - gt * a);
+            if (DELTA) u = gbc.y * (u - gt * a);
 #pragma unroll
             for (int i = 0; i < DPER; ++i) S[i] = S[i] * gt + kk[i] * u;
-            if (live && part == 0) o[((size_t)(base + tt) * H + h) * dv + j] = gt * b + u * c;
+            if (live && part == 0) *op = gt * b + u * c;
+            op += ostep;
         }
     }
     if (st) {
@@ -529,7 +547,7 @@ extern "C" int rg_state_scan(const float* q, int q_ld, const float* k, int k_ld,
     int chunk = DP > 128 ? 8 : 16;
     if (chunk > 4 * parts) chunk = 4 * parts;                      // what a thread prefetches of v stays in 4 registers
     if (chunk * CB > SCAN_MAX_PREFETCH * threads) return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)2 * chunk * (2 * DP + CB + 3) * sizeof(float);
+    const size_t smem = (size_t)2 * chunk * (2 * DP + CB + 4) * sizeof(float);
     if (smem > 48 * 1024 || H > 65535 || col_blocks > 65535) return RG_ERR_UNSUPPORTED;
     // 16-byte copies and state accesses where every row starts on a 16-byte boundary
     const int vec = d % 4 == 0 && q_ld % 4 == 0 && k_ld % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 &&
