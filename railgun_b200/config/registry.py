@@ -78,3 +78,5 @@ def _ensure_builtin():
         from ..models import rupulix  # noqa: F401
     if "Mepatar" not in _ARCHITECTURES:
         from ..models import mepatar  # noqa: F401
+    if "Kasarax" not in _ARCHITECTURES:
+        from ..models import kasarax  # noqa: F401

@@ -5,7 +5,10 @@
 // at positions [max(0, p - window + 1), p] and, with keep_first, also the first
 // keep_first positions of r whatever the window (kept tokens keep their own
 // positions), read from the paged cache through r's block table (the step's
-// own keys are written before it runs).
+// own keys are written before it runs).  Optional: `sink` [nh], one more term
+// exp(sink[h]) in head h's denominator that has neither key nor value and is
+// not scaled; `gate`, rows gate_ld apart, head h's output at token t is
+// multiplied by sigmoid(gate[t, h]).
 //
 // Formulas: kv_head = head / (nh / nkv); s_j = scale * q.k_j; running max m,
 // p_j = exp(s_j - m), out = sum p_j v_j / sum p_j
@@ -23,7 +26,8 @@ template <typename A>
 __global__ void paged_attention_general_kernel(
         const A* __restrict__ q, int q_stride, A* __restrict__ out, const A* __restrict__ kv_cache,
         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ req_of_token,
-        const int* __restrict__ positions, int nh, int nkv, int d, int page_size, int window, float scale, int keep_first) {
+        const int* __restrict__ positions, int nh, int nkv, int d, int page_size, int window, float scale, int keep_first,
+        const float* __restrict__ sink, const A* __restrict__ gate, int gate_ld) {
     extern __shared__ float smem[];
     float* qs = smem;                    // [d]
     float* ps = qs + d;                  // [ATT_THREADS]
@@ -81,7 +85,15 @@ __global__ void paged_attention_general_kernel(
         __syncthreads();
     }
     A* orow = out + ((size_t)t * nh + h) * d;
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (sink) {
+        const float m_new = fmaxf(m, sink[h]);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sink[h] - m_new);
+        acc0 *= alpha;
+        acc1 *= alpha;
+    }
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (gate) inv *= 1.f / (1.f + expf(-to_f32(gate[(size_t)t * gate_ld + h])));
     if (threadIdx.x < d) orow[threadIdx.x] = from_f32<A>(acc0 * inv);
     if (threadIdx.x + ATT_THREADS < d) orow[threadIdx.x + ATT_THREADS] = from_f32<A>(acc1 * inv);
 }
@@ -89,7 +101,8 @@ __global__ void paged_attention_general_kernel(
 extern "C" int rg_paged_attention_general(
         const void* q, int q_stride, void* out, const void* kv_cache, int dtype,
         const int* block_table, int max_blocks, const int* req_of_token, const int* positions,
-        int T, int nh, int nkv, int d, int page_size, int window, float scale, int keep_first, void* stream) {
+        int T, int nh, int nkv, int d, int page_size, int window, float scale, int keep_first, const float* sink,
+        const void* gate, int gate_ld, void* stream) {
     if (T <= 0) return 0;
     if (d > 2 * ATT_THREADS || d < 1 || nkv < 1 || nh < nkv || nh % nkv || keep_first < 0) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -98,10 +111,12 @@ extern "C" int rg_paged_attention_general(
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(paged_attention_general_kernel<bf16>, grid, dim3(ATT_THREADS), smem, s, 1,
                          (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks,
-                         req_of_token, positions, nh, nkv, d, page_size, window, scale, keep_first);
+                         req_of_token, positions, nh, nkv, d, page_size, window, scale, keep_first, sink, (const bf16*)gate,
+                         gate_ld);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(paged_attention_general_kernel<float>, grid, dim3(ATT_THREADS), smem, s, 1,
                          (const float*)q, q_stride, (float*)out, (const float*)kv_cache, block_table, max_blocks,
-                         req_of_token, positions, nh, nkv, d, page_size, window, scale, keep_first);
+                         req_of_token, positions, nh, nkv, d, page_size, window, scale, keep_first, sink, (const float*)gate,
+                         gate_ld);
     return RG_ERR_UNSUPPORTED;
 }

@@ -18,6 +18,10 @@
 // count chosen by the caller.  The prefill kernel has no counterpart: the
 // reference has no causal mask inside a portion of a prompt.
 //
+// Optional in both: `sink` [nh] (one more term exp(sink[h]) in head h's denominator, with neither key nor
+// value, unscaled, counted once: in the split kernel where the splits are added up) and `gate` (rows gate_ld
+// apart: head h's output at token t is multiplied by sigmoid(gate[t, h]) where it is divided by the denominator).
+//
 // Head sizes: any multiple of 16 up to 256, compiled in three register-size
 // classes (<= 64, <= 128, <= 256).  Any page size.  K/V tiles are gathered
 // row by row with cp.async (each key's page is looked up in the block table).
@@ -58,6 +62,18 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+// A sink of score `sink` (natural units) joins a softmax whose running maximum is M (log2 domain) and whose sum is
+// L: returns the factor on the accumulated output and updates L (M itself is not needed afterwards).
+__device__ __forceinline__ float join_sink(float sink, float M, float& L) {
+    const float sk = sink * 1.4426950408889634f;
+    const float Mn = fmaxf(M, sk);
+    const float a = exp2f(M - Mn);                   // 0 when M = -inf
+    L = L * a + exp2f(sk - Mn);
+    return a;
+}
+__device__ __forceinline__ float gate_of(const bf16* __restrict__ gate, int gate_ld, int t, int h) {
+    return gate ? 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)t * gate_ld + h]))) : 1.f;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -123,7 +139,8 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 64 ? 4 : (DMAX <= 128 ? 2 : 
 prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ kv_cache, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tiles, const int* __restrict__ positions, int nh, int nkv, int d_arg,
-                         int page_size, int page_shift, int window, int keep, float scale_log2) {
+                         int page_size, int page_shift, int window, int keep, float scale_log2,
+                         const float* __restrict__ sink, const bf16* __restrict__ gate, int gate_ld) {
     const int d = EXACT ? DMAX : d_arg;
     constexpr int KD = DMAX / 16;          // k-steps over the head dimension
     constexpr int ND = DMAX / 8;           // n-tiles of the output
@@ -294,8 +311,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    float f0 = 1.f, f1 = 1.f;
+    if (sink) { f0 = join_sink(sink[h], m0, l0); f1 = join_sink(sink[h], m1, l1); }
     const int lr0 = warp * 16 + g, lr1 = lr0 + 8;
+    if (gate) {
+        if (lr0 < nrows) f0 *= gate_of(gate, gate_ld, row0 + lr0, h);
+        if (lr1 < nrows) f1 *= gate_of(gate, gate_ld, row0 + lr1, h);
+    }
+    const float inv0 = l0 > 0.f ? f0 / l0 : 0.f, inv1 = l1 > 0.f ? f1 / l1 : 0.f;
 #pragma unroll
     for (int i = 0; i < ND; ++i) {
         if (i < d8) {
@@ -333,7 +356,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                         float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
                         int* __restrict__ counters, int nh, int nkv, int d_arg,
                         int page_size, int page_shift, int window, int keep, float scale_log2, int num_splits,
-                        int head_tiles, int cluster_merge) {
+                        int head_tiles, int cluster_merge, const float* __restrict__ sink,
+                        const bf16* __restrict__ gate, int gate_ld) {
     const int d = EXACT ? DMAX : d_arg;
     __shared__ int is_last;
     constexpr int KD = DMAX / 16;
@@ -404,7 +428,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                 L += w * __ldcg(part_ml + (base + s2) * 2 + 1);
                 if (w > 0.f) acc += w * __ldcg(part_o + (base + s2) * d + col);
             }
-            const float inv = L > 0.f ? 1.f / L : 0.f;
+            if (sink) acc *= join_sink(sink[h0 + row], M, L);
+            const float inv = L > 0.f ? gate_of(gate, gate_ld, t, h0 + row) / L : 0.f;
             out[((size_t)t * nh + h0 + row) * d + col] = __float2bfloat16_rn(acc * inv);
         }
     };
@@ -669,7 +694,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             L += sc * cML[(w * DEC_HEADS + row) * 2 + 1];
         }
         if (num_splits == 1 && counters != nullptr) {               // the only split: this is the result
-            const float inv = L > 0.f ? 1.f / L : 0.f;
+            if (sink) acc *= join_sink(sink[h0 + row], M, L);
+            const float inv = L > 0.f ? gate_of(gate, gate_ld, t, h0 + row) / L : 0.f;
             out[((size_t)t * nh + h0 + row) * d + col] = __float2bfloat16_rn(acc * inv);
         } else if (cluster_merge) {
             fin_o[row * d + col] = acc;
@@ -687,7 +713,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
 // out[t, h, :] = sum_s 2^{m_s - M} o_s / sum_s 2^{m_s - M} l_s
 __global__ void decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      bf16* __restrict__ out, const int* __restrict__ rows, int nh, int d,
-                                     int num_splits) {
+                                     int num_splits, const float* __restrict__ sink, const bf16* __restrict__ gate,
+                                     int gate_ld) {
     pdl_wait();
     pdl_trigger();
     const int ti = blockIdx.x, h = blockIdx.y;
@@ -698,7 +725,8 @@ __global__ void decode_reduce_kernel(const float* __restrict__ part_o, const flo
     const float Ms = M == -INFINITY ? 0.f : M;
     float L = 0.f;
     for (int s = 0; s < num_splits; ++s) L += exp2f(part_ml[(base + s) * 2] - Ms) * part_ml[(base + s) * 2 + 1];
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const float fs = sink ? join_sink(sink[h], M, L) : 1.f;
+    const float inv = L > 0.f ? fs * gate_of(gate, gate_ld, t, h) / L : 0.f;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < num_splits; ++s) {
@@ -722,11 +750,13 @@ template <typename K> static int allow_smem(K kernel, size_t bytes) {
     return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-// keep_first: with a window, the first positions of a request that every later query still sees
-extern "C" int rg_prefill_attention_keep(const void* q, int q_stride, void* out, const void* kv_cache,
+// keep_first: with a window, the first positions of a request that every later query still sees; sink [nh] and
+// gate (rows gate_ld apart) may be null
+extern "C" int rg_prefill_attention_sink(const void* q, int q_stride, void* out, const void* kv_cache,
                                          const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                          const int* positions, int nh, int nkv, int d, int page_size, int window,
-                                         int keep_first, float scale, void* stream) {
+                                         int keep_first, float scale, const float* sink, const void* gate, int gate_ld,
+                                         void* stream) {
     if (n_tiles <= 0) return 0;
     if (keep_first < 0) return RG_ERR_UNSUPPORTED;
     if (d % 16 || d < 16 || d > 256 || nkv < 1 || nh < nkv || nh % nkv || (long long)n_tiles * nh > 0x7fffffffll)
@@ -740,10 +770,18 @@ extern "C" int rg_prefill_attention_keep(const void* q, int q_stride, void* out,
 #define RG_PREFILL(DM, EX) { int e = allow_smem(prefill_attention_kernel<DM, EX>, smem); if (e) return e; \
     return rg_launch(prefill_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
         (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, page_shift, \
-        window, window > 0 ? keep_first : 0, scale_log2); }
+        window, window > 0 ? keep_first : 0, scale_log2, sink, (const bf16*)gate, gate_ld); }
     if (d == 64) RG_PREFILL(64, true) else if (d == 128) RG_PREFILL(128, true)
     else if (d < 64) RG_PREFILL(64, false) else if (d < 128) RG_PREFILL(128, false) else RG_PREFILL(256, false)
 #undef RG_PREFILL
+}
+
+extern "C" int rg_prefill_attention_keep(const void* q, int q_stride, void* out, const void* kv_cache,
+                                         const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                                         const int* positions, int nh, int nkv, int d, int page_size, int window,
+                                         int keep_first, float scale, void* stream) {
+    return rg_prefill_attention_sink(q, q_stride, out, kv_cache, block_table, max_blocks, tiles, n_tiles, positions, nh,
+                                     nkv, d, page_size, window, keep_first, scale, nullptr, nullptr, 0, stream);
 }
 
 extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, const void* kv_cache,
@@ -758,7 +796,8 @@ static int rg_decode_attention_any(const void* q, int q_stride, void* out, const
                                    const int* block_table, int max_blocks, const int* rows, int n_tokens,
                                    const int* req_of_token, const int* positions, float* part_o, float* part_ml,
                                    int* counters, int nh, int nkv, int d, int page_size, int window, float scale,
-                                   int num_splits, int cluster_merge, void* stream, int keep_first = 0);
+                                   int num_splits, int cluster_merge, void* stream, int keep_first = 0,
+                                   const float* sink = nullptr, const void* gate = nullptr, int gate_ld = 0);
 
 // Scratch the caller provides: part_o floats = n_tokens * nh * num_splits * d; part_ml = n_tokens * nh * num_splits * 2.
 // counters: NULL (a second kernel reduces the splits), or n_tokens * nkv * ceil(group / 8) ints that are zero on
@@ -785,6 +824,19 @@ extern "C" int rg_decode_attention_keep(const void* q, int q_stride, void* out, 
                                    0, stream, keep_first);
 }
 
+// sink [nh] and gate (rows gate_ld apart) may be null
+extern "C" int rg_decode_attention_sink(const void* q, int q_stride, void* out, const void* kv_cache,
+                                        const int* block_table, int max_blocks, const int* rows, int n_tokens,
+                                        const int* req_of_token, const int* positions, float* part_o, float* part_ml,
+                                        int* counters, int nh, int nkv, int d, int page_size, int window,
+                                        int keep_first, float scale, int num_splits, const float* sink, const void* gate,
+                                        int gate_ld, void* stream) {
+    if (keep_first < 0) return RG_ERR_UNSUPPORTED;
+    return rg_decode_attention_any(q, q_stride, out, kv_cache, block_table, max_blocks, rows, n_tokens, req_of_token,
+                                   positions, part_o, part_ml, counters, nh, nkv, d, page_size, window, scale, num_splits,
+                                   0, stream, keep_first, sink, gate, gate_ld);
+}
+
 // The same with the splits of every (token, head tile) as one thread-block cluster (2 to 8 splits): no scratch, no
 // counters, no second kernel; the blocks add their partial results through distributed shared memory, in split
 // order like the other two ways (the same bits).  Alone it is the fastest of the three (8 tokens, 1,024 keys, 4
@@ -805,8 +857,10 @@ static int rg_decode_attention_any(const void* q, int q_stride, void* out, const
                                    const int* block_table, int max_blocks, const int* rows, int n_tokens,
                                    const int* req_of_token, const int* positions, float* part_o, float* part_ml,
                                    int* counters, int nh, int nkv, int d, int page_size, int window, float scale,
-                                   int num_splits, int cluster_merge, void* stream, int keep_first) {
+                                   int num_splits, int cluster_merge, void* stream, int keep_first, const float* sink,
+                                   const void* gate, int gate_ld) {
     if (n_tokens <= 0) return 0;
+    if (cluster_merge && (sink || gate)) return RG_ERR_UNSUPPORTED;
     if (d % 16 || d < 16 || d > 256 || nkv < 1 || nh < nkv || nh % nkv || num_splits < 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -824,7 +878,7 @@ static int rg_decode_attention_any(const void* q, int q_stride, void* out, const
         (const bf16*)q, q_stride, \
         (const bf16*)kv_cache, block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, (bf16*)out, \
         counters, nh, nkv, d, page_size, page_shift, window, window > 0 ? keep_first : 0, scale_log2, num_splits, \
-        head_tiles, cluster_merge); }
+        head_tiles, cluster_merge, sink, (const bf16*)gate, gate_ld); }
     if (d == 64) RG_DECODE(64, true) else if (d == 128) RG_DECODE(128, true)
     else if (d < 64) RG_DECODE(64, false) else if (d < 128) RG_DECODE(128, false) else RG_DECODE(256, false)
 #undef RG_DECODE
@@ -832,7 +886,7 @@ static int rg_decode_attention_any(const void* q, int q_stride, void* out, const
     dim3 rgrid(n_tokens, nh);
     RgStreamOrder in_order(true);       // measured: the merge starting early, beside the splits, costs a batch-8 step 4 %
     return rg_launch(decode_reduce_kernel, rgrid, dim3(d >= 128 ? 128 : 64), 0, s, 1, (const float*)part_o,
-                     (const float*)part_ml, (bf16*)out, rows, nh, d, num_splits);
+                     (const float*)part_ml, (bf16*)out, rows, nh, d, num_splits, sink, (const bf16*)gate, gate_ld);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -85,6 +85,14 @@ __device__ __forceinline__ float gated_act(float g, float u, int kind, float lim
     return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
 }
 
+// Activations without a gate, in 32-bit.  kind 0: the square of relu; 1: relu; 2: gelu (tanh form); 3: silu.
+__device__ __forceinline__ float plain_act(float v, int kind) {
+    if (kind == 0) { const float r = fmaxf(v, 0.f); return r * r; }
+    if (kind == 1) return fmaxf(v, 0.f);
+    if (kind == 2) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v / (1.f + expf(-v));
+}
+
 #define RG_LAUNCH_RESULT() ((int)cudaGetLastError())
 
 // Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel before it

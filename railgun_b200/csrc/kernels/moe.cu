@@ -1,7 +1,7 @@
 // Routed experts: the router, the grouping of (token, choice) pairs by expert, the experts' products over
 // those groups, and the weighted sum.
 //
-//   z = W_r h (32-bit), s = softmax(z) over all N router outputs
+//   z = W_r h (32-bit), s = softmax(z) over all N router outputs (or, scoring 1, s = sigmoid(z), each on its own)
 //   the `top` outputs with the largest s + correction are chosen; their weights are s / (sum of the chosen s
 //   + 1e-20).  Outputs E..N-1 stand for identity experts (the expert's result is h itself); outputs 0..E-1
 //   for gated experts  down(silu(gate h) * (up h)).
@@ -22,7 +22,8 @@
 template <typename A>
 __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restrict__ router,
                                  const float* __restrict__ correction, int* __restrict__ ids,
-                                 float* __restrict__ weights, int T, int W, int N, int top, int renormalize) {
+                                 float* __restrict__ weights, int T, int W, int N, int top, int renormalize,
+                                 int scoring) {
     extern __shared__ float sm[];                 // per token of the block: N scores, N choice scores
     pdl_wait();
     pdl_trigger();
@@ -74,14 +75,22 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
         const int t = t0 + j;
         float* s = base + (size_t)j * 2 * N;
         float* c = s + N;
-        float mx = -INFINITY;
-        for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int n = lane; n < N; n += 32) { const float e = expf(s[n] - mx); s[n] = e; sum += e; }
-        sum = warp_sum(sum);
-        const float inv = 1.f / sum;
-        for (int n = lane; n < N; n += 32) { const float p = s[n] * inv; s[n] = p; c[n] = p + (correction ? correction[n] : 0.f); }
+        if (scoring == 1) {
+            for (int n = lane; n < N; n += 32) {
+                const float p = 1.f / (1.f + expf(-s[n]));
+                s[n] = p;
+                c[n] = p + (correction ? correction[n] : 0.f);
+            }
+        } else {
+            float mx = -INFINITY;
+            for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int n = lane; n < N; n += 32) { const float e = expf(s[n] - mx); s[n] = e; sum += e; }
+            sum = warp_sum(sum);
+            const float inv = 1.f / sum;
+            for (int n = lane; n < N; n += 32) { const float p = s[n] * inv; s[n] = p; c[n] = p + (correction ? correction[n] : 0.f); }
+        }
         __syncwarp();
         float chosen_sum = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -112,9 +121,9 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
 }
 
 extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const float* correction, int* ids,
-                            float* weights, int T, int W, int N, int top, int renormalize, void* stream) {
+                            float* weights, int T, int W, int N, int top, int renormalize, int scoring, void* stream) {
     if (T <= 0) return 0;
-    if (top < 1 || top > N) return RG_ERR_UNSUPPORTED;
+    if (top < 1 || top > N || scoring < 0 || scoring > 1) return RG_ERR_UNSUPPORTED;
     const size_t smem = (size_t)ROUTE_TOKENS * 2 * N * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -122,10 +131,10 @@ extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const
     dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(warps * 32);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(moe_route_kernel<bf16>, grid, block, smem, s, 1, (const bf16*)x, router, correction, ids,
-                         weights, T, W, N, top, renormalize);
+                         weights, T, W, N, top, renormalize, scoring);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(moe_route_kernel<float>, grid, block, smem, s, 1, (const float*)x, router, correction, ids,
-                         weights, T, W, N, top, renormalize);
+                         weights, T, W, N, top, renormalize, scoring);
     return RG_ERR_UNSUPPORTED;
 }
 
@@ -199,7 +208,8 @@ extern "C" int rg_moe_align(const int* ids, int P, int E, int tile_rows, int* so
 // One tile of the list: rows [first, first + n) of expert e.  Row `pos` of A is a[src[pos] / src_div] when
 // src is given (the token of the pair at that place), else a[pos].  w: [E, (GATED ? 2 N : N), K], the gated
 // form holding N gate rows and then N up rows per expert; out[pos, n] = sum_k a_k w_nk, or with GATED
-// silu(gate) * up.  32-bit accumulation in the order of k.
+// silu(gate) * up.  Without a gate, act >= 0 names an activation on the product (plain_act); -1: none.  32-bit
+// accumulation in the order of k.
 #define GG_BM 32
 #define GG_BN 64
 #define GG_BK 32
@@ -262,6 +272,7 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(
             if (n >= N) continue;
             float v = acc[i][j];
             if (GATED) v = gated_act(v, acc2[i][j], act, limit);
+            else if (act >= 0) v = plain_act(v, act);
             out[(size_t)(first + r) * ldo + n] = from_f32<A>(v);
         }
     }
@@ -284,7 +295,7 @@ extern "C" int rg_moe_grouped_gemm(const void* a, int lda, const int* src, int s
     return RG_ERR_UNSUPPORTED;
 }
 
-// out[t] (32-bit) = sum_k weights[t, k] * (ids[t, k] < E ? y[pair_pos[t, k]] : x[t])  (+ shared[t])
+// out[t] (32-bit) = sum_k weights[t, k] * (ids[t, k] < E ? y[pair_pos[t, k]] : x[t])  (+ shared[t]); weights null: all 1
 template <typename A>
 __global__ void moe_combine_kernel(const A* __restrict__ x, const A* __restrict__ y, const A* __restrict__ shared,
                                    const int* __restrict__ ids, const float* __restrict__ weights,
@@ -297,7 +308,7 @@ __global__ void moe_combine_kernel(const A* __restrict__ x, const A* __restrict_
     int* crow = reinterpret_cast<int*>(csm + top);
     for (int k = threadIdx.x; k < top; k += blockDim.x) {
         const size_t p = (size_t)t * top + k;
-        cw[k] = weights[p];
+        cw[k] = weights ? weights[p] : 1.f;
         crow[k] = ids[p] < E ? pair_pos[p] : -1;
     }
     __syncthreads();
@@ -342,6 +353,37 @@ __global__ void moe_gather_rows_kernel(const bf16* __restrict__ a, int lda, cons
     const uint4* from = reinterpret_cast<const uint4*>(a + (size_t)(pair / src_div) * lda);
     uint4* to = reinterpret_cast<uint4*>(out + (size_t)pos * K);
     for (int i = threadIdx.x; i < (K >> 3); i += blockDim.x) to[i] = from[i];
+}
+
+// out[pos] = scale[src[pos]] * a[src[pos] / src_div]: the same rows, each times its pair's weight (32-bit product,
+// one rounding), for experts whose weight multiplies their input.  Any K and either storage type.
+template <typename A>
+__global__ void moe_gather_scaled_rows_kernel(const A* __restrict__ a, int lda, const int* __restrict__ src, int src_div,
+                                              const float* __restrict__ scale, A* __restrict__ out, int K) {
+    pdl_wait();
+    pdl_trigger();
+    const int pos = blockIdx.x;
+    const int pair = src[pos];
+    if (pair < 0) return;
+    const float f = scale[pair];
+    const A* from = a + (size_t)(pair / src_div) * lda;
+    A* to = out + (size_t)pos * K;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) to[i] = from_f32<A>(f * to_f32(from[i]));
+}
+
+extern "C" int rg_moe_gather_scaled_rows(const void* a, int dtype, int lda, const int* src, int src_div,
+                                         const float* scale, void* out, int P, int K, void* stream) {
+    if (P <= 0) return 0;
+    if (src_div < 1 || K < 1) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = K >= 1024 ? 256 : 128;
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(moe_gather_scaled_rows_kernel<bf16>, dim3(P), dim3(threads), 0, s, 1, (const bf16*)a, lda, src,
+                         src_div, scale, (bf16*)out, K);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(moe_gather_scaled_rows_kernel<float>, dim3(P), dim3(threads), 0, s, 1, (const float*)a, lda, src,
+                         src_div, scale, (float*)out, K);
+    return RG_ERR_UNSUPPORTED;
 }
 
 extern "C" int rg_moe_gather_rows(const void* a, int lda, const int* src, int src_div, void* out, int P, int K,
@@ -471,6 +513,7 @@ __global__ void __launch_bounds__(BM == 128 ? 256 : 128) moe_grouped_gemm_mma_ke
                     if (n >= N) continue;
                     float v = acc[0][mi][ni][half * 2 + c];
                     if (GATED) v = gated_act(v, acc[NB - 1][mi][ni][half * 2 + c], act, limit);
+                    else if (act >= 0) v = plain_act(v, act);
                     orow[n] = __float2bfloat16_rn(v);
                 }
             }

@@ -373,3 +373,77 @@ extern "C" int rg_add_group_rmsnorm(float* resid, const void* p1, int p1_dtype, 
                          p2_dtype, w1, w2, eps, (float*)out1, (float*)out2, rows, H, groups, wpt);
     return RG_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The sum of several rows, each first RMS-normed with a weight and a constant of its own:
+//   out[t] (32-bit) = sum_b c_b * y_b[t] / sqrt(mean(y_b[t]^2) + eps) * w_b
+// for branches that run side by side and are brought to one size before they are added.  One block per row;
+// a thread keeps its numbers of every input in registers between the two passes (up to NS_KEEP per input).
+// ---------------------------------------------------------------------------------------------------
+#define NS_MAX 4
+#define NS_KEEP 8
+struct NormSumArgs {
+    const void* y[NS_MAX];
+    const float* w[NS_MAX];
+    float c[NS_MAX];
+    int n;
+};
+
+template <typename P>
+__global__ void __launch_bounds__(256) norm_sum_kernel(NormSumArgs a, float eps, float* __restrict__ out, int H) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const size_t base = (size_t)blockIdx.x * H;
+    float acc[NS_KEEP];
+#pragma unroll
+    for (int j = 0; j < NS_KEEP; ++j) acc[j] = 0.f;
+    for (int b = 0; b < a.n; ++b) {
+        const P* y = reinterpret_cast<const P*>(a.y[b]) + base;
+        float keep[NS_KEEP];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NS_KEEP; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            keep[j] = i < H ? to_f32(y[i]) : 0.f;
+            ss += keep[j] * keep[j];
+        }
+        for (int i = threadIdx.x + NS_KEEP * blockDim.x; i < H; i += blockDim.x) { const float v = to_f32(y[i]); ss += v * v; }
+        ss = block_sum(ss, scratch);
+        const float f = rsqrtf(ss / (float)H + eps) * a.c[b];
+        const float* w = a.w[b];
+#pragma unroll
+        for (int j = 0; j < NS_KEEP; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < H) acc[j] += keep[j] * f * w[i];
+        }
+        for (int i = threadIdx.x + NS_KEEP * blockDim.x; i < H; i += blockDim.x) {
+            const float v = to_f32(y[i]) * f * w[i];
+            if (b == 0) out[base + i] = v; else out[base + i] += v;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NS_KEEP; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < H) out[base + i] = acc[j];
+    }
+}
+
+// ys, ws: n pointers each (rows of H numbers of type `dtype`; weights [H] float); cs: n constants.
+extern "C" int rg_norm_sum(const void* const* ys, const float* const* ws, const float* cs, int n, int dtype, float eps,
+                           float* out, int T, int H, void* stream) {
+    if (T <= 0) return 0;
+    if (n < 1 || n > NS_MAX || H < 1) return RG_ERR_UNSUPPORTED;
+    NormSumArgs a;
+    a.n = n;
+    for (int b = 0; b < NS_MAX; ++b) {
+        a.y[b] = b < n ? ys[b] : nullptr;
+        a.w[b] = b < n ? ws[b] : nullptr;
+        a.c[b] = b < n ? cs[b] : 0.f;
+    }
+    const int threads = H >= 2048 ? 256 : (H >= 512 ? 128 : 64);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RG_DTYPE_BF16) return rg_launch(norm_sum_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, a, eps, out, H);
+    if (dtype == RG_DTYPE_F32) return rg_launch(norm_sum_kernel<float>, dim3(T), dim3(threads), 0, s, 1, a, eps, out, H);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -193,11 +193,12 @@ extern "C" int rg_conv_state_update(const void* x, int x_dtype, int ld, int x_of
 }
 
 // proj rows: [q (H d) | k (H d) | ...] at q_off and k_off.  q_out, k_out [T, H, d] float.  freq: dims / 2 (64-bit).
+// act 1: silu on q and k (before the rotation) and, with v_out [T, H dv] float, on the H dv numbers at v_off too.
 template <typename A>
 __global__ void retention_prepare_kernel(const A* __restrict__ proj, int ld, int q_off, int k_off,
                                          const double* __restrict__ freq, int dims, const int* __restrict__ positions,
                                          float* __restrict__ q_out, float* __restrict__ k_out, int H, int d,
-                                         float k_scale) {
+                                         float k_scale, int act, int v_off, int dv, float* __restrict__ v_out) {
     extern __shared__ float cs[];                    // cos | sin of the token's dims / 2 angles
     pdl_wait();
     pdl_trigger();
@@ -211,28 +212,39 @@ __global__ void retention_prepare_kernel(const A* __restrict__ proj, int ld, int
         const int which = e / (H * d), rem = e - which * H * d, h = rem / d, i = rem - h * d;
         const A* src = row + (which ? k_off : q_off) + (size_t)h * d;
         float v = to_f32(src[i]);
-        if (i < half) v = v * cs[i] - to_f32(src[i + half]) * cs[half + i];
-        else if (i < dims) v = v * cs[i - half] + to_f32(src[i - half]) * cs[i];
+        if (act) v *= sm_sigmoid(v);
+        if (i < dims) {
+            float m = to_f32(src[i < half ? i + half : i - half]);
+            if (act) m *= sm_sigmoid(m);
+            v = i < half ? v * cs[i] - m * cs[half + i] : v * cs[i - half] + m * cs[i];
+        }
         if (which) k_out[((size_t)t * H + h) * d + i] = v * k_scale;
         else q_out[((size_t)t * H + h) * d + i] = v;
+    }
+    if (v_out) {
+        for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
+            float v = to_f32(row[v_off + e]);
+            if (act) v *= sm_sigmoid(v);
+            v_out[(size_t)t * H * dv + e] = v;
+        }
     }
 }
 
 extern "C" int rg_retention_prepare(const void* proj, int dtype, int ld, int q_off, int k_off, const double* freq,
                                     int dims, const int* positions, float* q_out, float* k_out, int T, int H, int d,
-                                    float k_scale, void* stream) {
+                                    float k_scale, int act, int v_off, int dv, float* v_out, void* stream) {
     if (T <= 0) return 0;
-    if (dims < 0 || dims > d || (dims & 1) || H < 1 || d < 1) return RG_ERR_UNSUPPORTED;
+    if (dims < 0 || dims > d || (dims & 1) || H < 1 || d < 1 || act < 0 || act > 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)(dims > 0 ? dims : 1) * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     const int threads = 2 * H * d >= 512 ? 256 : 128;
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(retention_prepare_kernel<bf16>, dim3(T), dim3(threads), smem, s, 1, (const bf16*)proj, ld, q_off,
-                         k_off, freq, dims, positions, q_out, k_out, H, d, k_scale);
+                         k_off, freq, dims, positions, q_out, k_out, H, d, k_scale, act, v_off, dv, v_out);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(retention_prepare_kernel<float>, dim3(T), dim3(threads), smem, s, 1, (const float*)proj, ld,
-                         q_off, k_off, freq, dims, positions, q_out, k_out, H, d, k_scale);
+                         q_off, k_off, freq, dims, positions, q_out, k_out, H, d, k_scale, act, v_off, dv, v_out);
     return RG_ERR_UNSUPPORTED;
 }
 
@@ -576,11 +588,12 @@ extern "C" int rg_state_scan(const float* q, int q_ld, const float* k, int k_ld,
 }
 
 // o [T, H, dv] float; gate: rows gate_ld apart (type A), head h at column gate_off + h dv; weight [dv] or null.
-// out [T, H dv] (type A) = o / sqrt(mean(o^2) + eps) * weight * silu(gate).  One warp per (token, head).
+// out [T, H dv] (type A) = o / sqrt(mean(o^2) + eps) * weight * silu(gate) (gate_kind 1: sigmoid(gate)).  One warp
+// per (token, head).
 template <typename A, typename O>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const A* __restrict__ gate, int gate_ld, int gate_off,
                                       const float* __restrict__ weight, float eps, O* __restrict__ out, int T, int H,
-                                      int dv) {
+                                      int dv, int gate_kind) {
     pdl_wait();
     pdl_trigger();
     const int lane = threadIdx.x & 31;
@@ -595,22 +608,52 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const A* __re
     const A* grow = gate + (size_t)t * gate_ld + gate_off + (size_t)h * dv;
     for (int i = lane; i < dv; i += 32) {
         const float z = to_f32(grow[i]);
-        out[(size_t)idx * dv + i] = from_f32<O>(src[i] * inv * (weight ? weight[i] : 1.f) * (z * sm_sigmoid(z)));
+        out[(size_t)idx * dv + i] = from_f32<O>(src[i] * inv * (weight ? weight[i] : 1.f) *
+                                                (gate_kind ? sm_sigmoid(z) : z * sm_sigmoid(z)));
     }
 }
 
+// The same with ONE root mean square over all H dv numbers of a token and a weight of that size: one block per token.
+template <typename A, typename O>
+__global__ void row_norm_gate_kernel(const float* __restrict__ o, const A* __restrict__ gate, int gate_ld, int gate_off,
+                                     const float* __restrict__ weight, float eps, O* __restrict__ out, int n,
+                                     int gate_kind) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const float* src = o + (size_t)t * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += src[i] * src[i];
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)n + eps);
+    const A* grow = gate + (size_t)t * gate_ld + gate_off;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float z = to_f32(grow[i]);
+        out[(size_t)t * n + i] = from_f32<O>(src[i] * inv * (weight ? weight[i] : 1.f) *
+                                             (gate_kind ? sm_sigmoid(z) : z * sm_sigmoid(z)));
+    }
+}
+
+// whole 0: every head normed on its own (weight [dv]); 1: all heads of a token together (weight [H dv]).
+// gate_kind 0: silu(gate); 1: sigmoid(gate).
 extern "C" int rg_head_norm_gate(const float* o, const void* gate, int gate_dtype, int gate_ld, int gate_off,
                                  const float* weight, float eps, void* out, int out_dtype, int T, int H, int dv,
-                                 void* stream) {
+                                 int whole, int gate_kind, void* stream) {
     if (T <= 0) return 0;
+    if (gate_kind < 0 || gate_kind > 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const long long n = (long long)T * H;
     dim3 grid((unsigned)((n + 3) / 4));
-#define SM_HNG(A, O) return rg_launch(head_norm_gate_kernel<A, O>, grid, dim3(128), 0, s, 1, o, (const A*)gate, gate_ld, \
-        gate_off, weight, eps, (O*)out, T, H, dv)
-    if (gate_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_BF16) SM_HNG(bf16, bf16);
-    if (gate_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_F32) SM_HNG(float, float);
-    if (gate_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_BF16) SM_HNG(float, bf16);
+    const int row = H * dv;
+    const int threads = row >= 1024 ? 256 : 128;
+#define SM_HNG(A, O) { if (whole) return rg_launch(row_norm_gate_kernel<A, O>, dim3(T), dim3(threads), 0, s, 1, o, \
+        (const A*)gate, gate_ld, gate_off, weight, eps, (O*)out, row, gate_kind); \
+        return rg_launch(head_norm_gate_kernel<A, O>, grid, dim3(128), 0, s, 1, o, (const A*)gate, gate_ld, \
+        gate_off, weight, eps, (O*)out, T, H, dv, gate_kind); }
+    if (gate_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_BF16) SM_HNG(bf16, bf16)
+    if (gate_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_F32) SM_HNG(float, float)
+    if (gate_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_BF16) SM_HNG(float, bf16)
 #undef SM_HNG
     return RG_ERR_UNSUPPORTED;
 }

@@ -201,6 +201,27 @@ def add_group_rmsnorm(resid: torch.Tensor, pending, weights, groups: int, eps: f
     return outs
 
 
+def norm_sum(ys, weights, consts, eps: float) -> torch.Tensor:
+    """float32 [T, H] = sum_b consts[b] * RMSNorm(ys[b]; weights[b], eps): up to four [T, H] tensors of one type,
+    each divided by its rows' root mean square, times its weight [H] (float32) and its constant, added in order."""
+    n = len(ys)
+    if not 1 <= n <= 4 or len(weights) != n or len(consts) != n:
+        raise KernelError("norm_sum: one to four inputs, each with a weight and a constant")
+    T, H = ys[0].shape
+    for y, w in zip(ys, weights):
+        _check(y, "y", ys[0].dtype)
+        _check(w, "weight", torch.float32)
+        if tuple(y.shape) != (T, H) or w.numel() != H:
+            raise KernelError(f"norm_sum: input {tuple(y.shape)} or weight of {w.numel()} does not match [{T}, {H}]")
+    out = torch.empty((T, H), dtype=torch.float32, device=ys[0].device)
+    yp = (c_void_p * n)(*[y.data_ptr() for y in ys])
+    wp = (c_void_p * n)(*[w.data_ptr() for w in weights])
+    cs = (c_float * n)(*[float(c) for c in consts])
+    _ok(_fn("norm", "rg_norm_sum")(yp, wp, cs, c_int(n), c_int(_dtype_code(ys[0])), c_float(eps), _ptr(out), c_int(T),
+                                   c_int(H), _stream()), "norm_sum")
+    return out
+
+
 class PendingNormed:
     """A part's output that is still to be RMS-normed (``weight``, ``eps``; the
     weight holds whatever constant factors follow the norm) before it is added
@@ -448,9 +469,14 @@ def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
 MOE_TILE_ROWS = 32
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, correction, top: int, renormalize: bool = True):
+MOE_SCORINGS = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction, top: int, renormalize: bool = True,
+              scoring: str = "softmax"):
     """Router of a mixture of experts: softmax of the 32-bit logits ``router`` x
-    over all N outputs; the ``top`` outputs with the largest score + correction
+    over all N outputs (``scoring`` "sigmoid": the sigmoid of each logit
+    instead); the ``top`` outputs with the largest score + correction
     (``correction`` None: the largest scores); weights = their scores over
     their sum, or with ``renormalize`` False the scores themselves.  Returns
     (ids int32 [T, top], weights float32 [T, top])."""
@@ -458,6 +484,8 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction, top: int, renor
     _check(router, "router", torch.float32)
     if correction is not None:
         _check(correction, "correction", torch.float32)
+    if scoring not in MOE_SCORINGS:
+        raise KernelError(f"moe_route: scoring {scoring!r} is not known; known: {sorted(MOE_SCORINGS)}")
     T, W = x.shape
     N = router.shape[0]
     if router.shape[1] != W or (correction is not None and correction.numel() != N):
@@ -466,7 +494,7 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction, top: int, renor
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
     _ok(_fn("moe", "rg_moe_route")(_ptr(x), c_int(_dtype_code(x)), _ptr(router), _ptr(correction), _ptr(ids),
                                    _ptr(weights), c_int(T), c_int(W), c_int(N), c_int(top), c_int(1 if renormalize else 0),
-                                   _stream()), "moe_route")
+                                   c_int(MOE_SCORINGS[scoring]), _stream()), "moe_route")
     return ids, weights
 
 
@@ -506,10 +534,12 @@ def gated_activation(gate_up: torch.Tensor, kind: str = "silu", limit: float = 0
 
 
 def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles: torch.Tensor, places: int,
-                     gated: bool, tile_rows: int = MOE_TILE_ROWS, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
+                     gated: bool, tile_rows: int = MOE_TILE_ROWS, act: str = "silu", limit: float = 0.0,
+                     plain_act: str | None = None) -> torch.Tensor:
     """out[pos] = W_e a_row(pos) for every place of the tile list, e the tile's
     expert; ``w`` [E, N, K] (``gated``: [E, 2 N, K] = gate rows then up rows and
-    out = silu(gate) * up).  Row ``pos`` of the input is ``a[src[pos] // src_div]``
+    out = silu(gate) * up, or another gated activation ``act``; not gated:
+    ``plain_act`` names an activation on the product, see ``ACTIVATIONS``).  Row ``pos`` of the input is ``a[src[pos] // src_div]``
     or, without ``src``, ``a[pos]``.  Returns [places, N]; rows that belong to no
     tile are not written.  bfloat16 with rows on 16-byte boundaries runs on the
     tensor cores (tiles of 32 places: mma.sync, weight-streaming; tiles of 128:
@@ -546,21 +576,25 @@ def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles:
             _ptr(a), c_int(a.stride(0)), c_int(places), _ptr(w), c_int(E), c_int(rows_w), c_int(K), _ptr(wide),
             c_int(rows_w), _ptr(tiles), c_int(tiles.shape[0]), _ptr(err), _stream()), "tc_gemm_grouped")
         if not gated:
-            return wide
+            return activation(wide, plain_act) if plain_act else wide
         return silu_mul(wide) if act == "silu" else gated_activation(wide, act, limit)
     if act not in GATED_ACTIVATIONS:
         raise KernelError(f"unknown gated activation {act!r}; known: {sorted(GATED_ACTIVATIONS)}")
+    if plain_act is not None and (gated or plain_act not in ACTIVATIONS):
+        raise KernelError(f"moe_grouped_gemm: activation {plain_act!r} on a product without a gate; known: "
+                          f"{sorted(ACTIVATIONS)}")
+    act_code = GATED_ACTIVATIONS[act] if gated else (ACTIVATIONS[plain_act] if plain_act else -1)
     out = torch.empty((places, N), dtype=a.dtype, device=a.device)
     if moe_grouped_gemm_tc_ok(a.dtype, K, a.stride(0)):
         _ok(_fn("moe", "rg_moe_grouped_gemm_mma")(
             _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), _ptr(tiles),
             c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0),
-            c_int(GATED_ACTIVATIONS[act]), c_float(limit), _stream()), "moe_grouped_gemm_mma")
+            c_int(act_code), c_float(limit), _stream()), "moe_grouped_gemm_mma")
         return out
     _ok(_fn("moe", "rg_moe_grouped_gemm")(
         _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), c_int(_dtype_code(a)),
         _ptr(tiles), c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0),
-        c_int(GATED_ACTIVATIONS[act]), c_float(limit), _stream()), "moe_grouped_gemm")
+        c_int(act_code), c_float(limit), _stream()), "moe_grouped_gemm")
     return out
 
 
@@ -576,11 +610,28 @@ def moe_tile_rows(dtype, pairs: int, num_experts: int, K1: int, K2: int) -> int:
     return 128 if tc and pairs >= 64 * max(1, num_experts) else MOE_TILE_ROWS
 
 
-def moe_combine(x: torch.Tensor, y, shared, ids: torch.Tensor, weights: torch.Tensor, pair_pos: torch.Tensor,
+def moe_scaled_rows(x: torch.Tensor, sorted_pair: torch.Tensor, top: int, weights: torch.Tensor,
+                    places: int) -> torch.Tensor:
+    """[places, W]: place ``pos`` holds weights[pair] * x[pair // top] for the pair ``sorted_pair[pos]`` (32-bit
+    product, one rounding): the input of experts whose weight multiplies what they read.  Places without a pair
+    are not written."""
+    _check_rows(x, "x")
+    _check(sorted_pair, "sorted_pair", torch.int32)
+    _check(weights, "weights", torch.float32)
+    if sorted_pair.numel() < places or weights.numel() != x.shape[0] * top:
+        raise KernelError("moe_scaled_rows: sizes do not match")
+    out = torch.empty((places, x.shape[1]), dtype=x.dtype, device=x.device)
+    _ok(_fn("moe", "rg_moe_gather_scaled_rows")(_ptr(x), c_int(_dtype_code(x)), c_int(x.stride(0)), _ptr(sorted_pair),
+                                                c_int(top), _ptr(weights), _ptr(out), c_int(places), c_int(x.shape[1]),
+                                                _stream()), "moe_scaled_rows")
+    return out
+
+
+def moe_combine(x: torch.Tensor, y, shared, ids: torch.Tensor, weights, pair_pos: torch.Tensor,
                 num_experts: int) -> torch.Tensor:
     """float32 [T, W] = sum over a token's choices of weight * (the expert's
     row of ``y``, or the token's own row of ``x`` for a choice with no expert
-    behind it), plus ``shared`` if given."""
+    behind it), plus ``shared`` if given.  ``weights`` None: every weight is 1."""
     _check(x, "x")
     T, W = x.shape
     top = ids.shape[1]
@@ -867,22 +918,28 @@ def conv_state_update(x: torch.Tensor, x_off: int, state: torch.Tensor, batch) -
 
 
 def retention_prepare(proj: torch.Tensor, q_off: int, k_off: int, freq: torch.Tensor, rot_dims: int,
-                      positions: torch.Tensor, H: int, d: int, k_scale: float):
+                      positions: torch.Tensor, H: int, d: int, k_scale: float, silu: bool = False, v_off: int = -1,
+                      dv: int = 0):
     """q, k [T, H, d] float32 from the columns of ``proj`` at ``q_off`` and ``k_off``: the first ``rot_dims`` numbers
-    of every head rotated in pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64), k times ``k_scale``."""
+    of every head rotated in pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64), k times ``k_scale``.
+    ``silu``: the activation on q and k (before the rotation).  With ``v_off`` >= 0 also v [T, H dv] float32 from
+    the columns at ``v_off``, with the same activation; returns (q, k) or (q, k, v)."""
     _check_rows(proj, "proj")
     _check(freq, "freq", torch.float64)
     _check(positions, "positions", torch.int32)
     T = proj.shape[0]
-    if proj.shape[1] < max(q_off, k_off) + H * d or freq.numel() < rot_dims // 2:
+    if proj.shape[1] < max(q_off, k_off) + H * d or freq.numel() < rot_dims // 2 or (
+            v_off >= 0 and (dv < 1 or proj.shape[1] < v_off + H * dv)):
         raise KernelError("retention_prepare: sizes do not match")
     q = torch.empty((T, H, d), dtype=torch.float32, device=proj.device)
     k = torch.empty((T, H, d), dtype=torch.float32, device=proj.device)
+    v = torch.empty((T, H * dv), dtype=torch.float32, device=proj.device) if v_off >= 0 else None
     _ok(_fn("state_mixers", "rg_retention_prepare")(
         _ptr(proj), c_int(_dtype_code(proj)), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), _ptr(freq),
-        c_int(rot_dims), _ptr(positions), _ptr(q), _ptr(k), c_int(T), c_int(H), c_int(d), c_float(k_scale), _stream()),
+        c_int(rot_dims), _ptr(positions), _ptr(q), _ptr(k), c_int(T), c_int(H), c_int(d), c_float(k_scale),
+        c_int(1 if silu else 0), c_int(max(v_off, 0)), c_int(dv), _ptr(v), _stream()),
         "retention_prepare")
-    return q, k
+    return (q, k) if v is None else (q, k, v)
 
 
 def delta_prepare(qkv: torch.Tensor, G: int, d: int, q_scale: float, unit_eps: float, ab: torch.Tensor, b_off: int,
@@ -949,40 +1006,59 @@ def state_scan_rows(rows: int) -> None:
     _fn("state_mixers", "rg_state_scan_rows")(c_int(rows))
 
 
-def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight, eps: float, out_dtype) -> torch.Tensor:
+HEAD_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight, eps: float, out_dtype, whole: bool = False,
+                   gate_kind: str = "silu") -> torch.Tensor:
     """[T, H dv] in ``out_dtype``: every head of ``o`` [T, H, dv] (float32) divided by its root mean square (``eps``
-    inside the root), times ``weight`` [dv] (None: no weight), times silu(``gate``) ([T, H dv] view)."""
+    inside the root), times ``weight`` [dv] (None: no weight), times silu(``gate``) ([T, H dv] view) or, with
+    ``gate_kind`` "sigmoid", sigmoid(``gate``).  ``whole``: one root mean square over all H dv numbers of a token
+    and a weight of that size."""
     _check(o, "o", torch.float32)
     _check_rows(gate, "gate")
     T, H, dv = o.shape
     if gate.shape != (T, H * dv):
         raise KernelError(f"head_norm_gate: gate {tuple(gate.shape)} vs o {tuple(o.shape)}")
+    if gate_kind not in HEAD_GATES:
+        raise KernelError(f"head_norm_gate: gate {gate_kind!r} is not known; known: {sorted(HEAD_GATES)}")
     if weight is not None:
         _check(weight, "weight", torch.float32)
-        if weight.numel() != dv:
-            raise KernelError(f"head_norm_gate: weight has {weight.numel()} elements, heads have {dv}")
+        if weight.numel() != (H * dv if whole else dv):
+            raise KernelError(f"head_norm_gate: weight has {weight.numel()} elements, expected "
+                              f"{H * dv if whole else dv}")
     out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
     _ok(_fn("state_mixers", "rg_head_norm_gate")(
         _ptr(o), _ptr(gate), c_int(_dtype_code(gate)), c_int(gate.stride(0)), c_int(0), _ptr(weight), c_float(eps),
-        _ptr(out), c_int(_dtype_code(out)), c_int(T), c_int(H), c_int(dv), _stream()), "head_norm_gate")
+        _ptr(out), c_int(_dtype_code(out)), c_int(T), c_int(H), c_int(dv), c_int(1 if whole else 0),
+        c_int(HEAD_GATES[gate_kind]), _stream()), "head_norm_gate")
     return out
 
 
 def attention_prepare(qkv: torch.Tensor, kv_cache, q_norm, k_norm, eps: float, freq: torch.Tensor, rot_dims: int,
                       interleaved: bool, positions: torch.Tensor, slots, factor, H: int, G: int, d: int, dv: int,
-                      D: int) -> torch.Tensor:
-    """Per token of ``qkv`` [T, H d + G d + G dv]: q and k heads RMS-normed over d (``q_norm`` / ``k_norm`` [d]
-    float32, None: no norm), their first ``rot_dims`` numbers rotated in pairs (2i, 2i + 1) (``interleaved``) or
-    (i, i + rot_dims / 2) by position * ``freq[i]`` (float64), q head h times ``factor[h]`` (float32 [H] or None).
-    Returns q [T, H, D]; k and v go to place ``slots[t]`` of ``kv_cache`` [pages, 2, G, page, D] (negative slot
-    or None: no write).  D >= max(d, dv): the rest of every row is zeros."""
+                      D: int, norm_whole: bool = False, temp_coef: float = 0.0, temp_every: int = 0,
+                      out_dtype=None) -> torch.Tensor:
+    """Per token of ``qkv`` [T, H d + G d + G dv] (a view whose rows may be further apart): q and k RMS-normed,
+    per head over d (``q_norm`` / ``k_norm`` [d] float32) or, with ``norm_whole``, all q heads together and all k
+    heads together (weights [H d] and [G d]); None: no norm.  Then their first ``rot_dims`` numbers rotated in
+    pairs (2i, 2i + 1) (``interleaved``) or (i, i + rot_dims / 2) by position * ``freq[i]`` (float64), q head h
+    times ``factor[h]`` (float32 [H] or None) and, with ``temp_every`` > 0, times
+    1 + ``temp_coef`` ln(floor((position + 1) / ``temp_every``) + 1).
+    Returns q [T, H, D] in ``out_dtype`` (default: qkv's; 32-bit rows may be rounded to bfloat16 here, once); k and
+    v go to place ``slots[t]`` of ``kv_cache`` [pages, 2, G, page, D] of that type (negative slot or None: no
+    write).  D >= max(d, dv): the rest of every row is zeros."""
     _check_rows(qkv, "qkv")
     _check(freq, "freq", torch.float64)
     _check(positions, "positions", torch.int32)
     T = qkv.shape[0]
+    out_dtype = out_dtype or qkv.dtype
     if qkv.shape[1] != (H + G) * d + G * dv or positions.numel() != T or freq.numel() < rot_dims // 2:
         raise KernelError(f"attention_prepare: qkv {tuple(qkv.shape)} does not match {H} + {G} heads of {d}, values of {dv}")
-    for w, name, n in ((q_norm, "q_norm", d), (k_norm, "k_norm", d), (factor, "factor", H)):
+    if out_dtype != qkv.dtype and qkv.dtype != torch.float32:
+        raise KernelError("attention_prepare: only 32-bit rows can be written in another type")
+    for w, name, n in ((q_norm, "q_norm", H * d if norm_whole else d), (k_norm, "k_norm", G * d if norm_whole else d),
+                       (factor, "factor", H)):
         if w is not None:
             _check(w, name, torch.float32)
             if w.numel() != n:
@@ -990,17 +1066,35 @@ def attention_prepare(qkv: torch.Tensor, kv_cache, q_norm, k_norm, eps: float, f
     page_size = 1
     if slots is not None:
         _check(slots, "slots", torch.int32)
-        _check(kv_cache, "kv_cache", qkv.dtype)
+        _check(kv_cache, "kv_cache", out_dtype)
         page_size = kv_cache.shape[3]
         if tuple(kv_cache.shape[1:]) != (2, G, page_size, D):
             raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match {G} heads of {D}")
-    q = torch.empty((T, H, D), dtype=qkv.dtype, device=qkv.device)
+    q = torch.empty((T, H, D), dtype=out_dtype, device=qkv.device)
     _ok(_fn("attention_prepare", "rg_attention_prepare")(
-        _ptr(qkv), c_int(_dtype_code(qkv)), c_int(qkv.stride(0)), _ptr(q), _ptr(kv_cache if slots is not None else None),
-        _ptr(q_norm), _ptr(k_norm), c_float(eps), _ptr(freq), c_int(rot_dims), c_int(1 if interleaved else 0),
-        _ptr(positions), _ptr(slots), _ptr(factor), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv), c_int(D),
+        _ptr(qkv), c_int(_dtype_code(qkv)), c_int(qkv.stride(0)), _ptr(q), c_int(_dtype_code(q)),
+        _ptr(kv_cache if slots is not None else None),
+        _ptr(q_norm), _ptr(k_norm), c_int(1 if norm_whole else 0), c_float(eps), _ptr(freq), c_int(rot_dims),
+        c_int(1 if interleaved else 0), _ptr(positions), _ptr(slots), _ptr(factor), c_float(temp_coef),
+        c_int(temp_every), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv), c_int(D),
         c_int(page_size), _stream()), "attention_prepare")
     return q
+
+
+def _sink_and_gate(sink, gate, nh: int, T: int, dtype):
+    """Checks of the attention kernels' optional ``sink`` [heads] float32 (exp(sink[h]) joins head h's softmax
+    denominator, once, unscaled, with neither key nor value) and ``gate`` ([T, heads] view in the kernels' storage
+    type: head h's output at token t is multiplied by sigmoid(gate[t, h])).  Returns the gate's row stride."""
+    if sink is not None:
+        _check(sink, "sink", torch.float32)
+        if sink.numel() != nh:
+            raise KernelError(f"{sink.numel()} sinks for {nh} heads")
+    if gate is None:
+        return 0
+    _check_rows(gate, "gate", dtype)
+    if gate.shape[0] < T or gate.shape[1] != nh:
+        raise KernelError(f"gate {tuple(gate.shape)} does not match {T} tokens of {nh} heads")
+    return gate.stride(0)
 
 
 ACTIVATIONS = {"relu2": 0, "relu": 1, "gelu_tanh": 2, "silu": 3}
@@ -1278,11 +1372,11 @@ def skinny_rope_ok(x, weight: torch.Tensor, d: int) -> bool:
 
 def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tensor, block_table: torch.Tensor,
                             req_of_token: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int, d: int,
-                            window: int, scale: float, keep_first: int = 0) -> torch.Tensor:
+                            window: int, scale: float, keep_first: int = 0, sink=None, gate=None) -> torch.Tensor:
     """The general attention kernel: out [T, nh*d].  ``q`` may be a view whose
     rows are ``q_stride`` elements apart (the q part of a fused qkv buffer).
     ``keep_first``: with a window, the first positions of a request that every
-    later query still sees."""
+    later query still sees.  ``sink``, ``gate``: see ``_sink_and_gate``."""
     if not q.is_cuda:
         raise KernelError("q must be a CUDA tensor (there is no CPU path)")
     _check(kv_cache, "kv_cache", q.dtype)
@@ -1296,10 +1390,12 @@ def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tens
     if d > 256:
         raise KernelError(f"head size {d} is above the kernels' limit of 256")
     out = torch.empty((T, nh * d), dtype=q.dtype, device=q.device)
+    gate_ld = _sink_and_gate(sink, gate, nh, T, q.dtype)
     _ok(_fn("attention_general", "rg_paged_attention_general")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), c_int(_dtype_code(q)), _ptr(block_table),
         c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), c_int(T), c_int(nh), c_int(nkv),
-        c_int(d), c_int(page_size), c_int(window or 0), c_float(scale), c_int(keep_first if window else 0), _stream()),
+        c_int(d), c_int(page_size), c_int(window or 0), c_float(scale), c_int(keep_first if window else 0),
+        _ptr(sink), _ptr(gate), c_int(gate_ld), _stream()),
         "paged_attention_general")
     return out
 
@@ -1320,19 +1416,22 @@ def _check_paged(q, kv_cache, block_table, nkv, d):
 
 
 def prefill_attention(q, q_stride: int, out, kv_cache, block_table, tiles, positions, nh: int, nkv: int, d: int,
-                      window: int, scale: float, keep_first: int = 0) -> None:
+                      window: int, scale: float, keep_first: int = 0, sink=None, gate=None) -> None:
     """Flash-style attention for requests that bring several tokens: ``tiles``
     [n, 3] = (first row, rows <= 64, request index).  Writes the tiles' rows of
     ``out`` [T, nh*d].  ``keep_first``: with a window, the first positions of a
-    request that every later query still sees."""
+    request that every later query still sees.  ``sink``, ``gate``: see
+    ``_sink_and_gate``."""
     page_size = _check_paged(q, kv_cache, block_table, nkv, d)
     _check(tiles, "tiles", torch.int32)
     _check(positions, "positions", torch.int32)
     _check(out, "out", q.dtype)
-    _ok(_fn("attention_mma", "rg_prefill_attention_keep")(
+    gate_ld = _sink_and_gate(sink, gate, nh, out.shape[0], q.dtype)
+    _ok(_fn("attention_mma", "rg_prefill_attention_sink")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(tiles), c_int(tiles.shape[0]), _ptr(positions), c_int(nh), c_int(nkv), c_int(d), c_int(page_size),
-        c_int(window or 0), c_int(keep_first if window else 0), c_float(scale), _stream()), "prefill_attention")
+        c_int(window or 0), c_int(keep_first if window else 0), c_float(scale), _ptr(sink), _ptr(gate), c_int(gate_ld),
+        _stream()), "prefill_attention")
 
 
 def decode_splits(n_tokens: int, kv_tiles: int, max_context: int) -> int:
@@ -1350,7 +1449,8 @@ _decode_counters: dict = {}
 
 def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_tokens: int, req_of_token, positions,
                      nh: int, nkv: int, d: int, window: int, scale: float, num_splits: int,
-                     scratch=None, fused_reduce=None, cluster: bool = False, keep_first: int = 0) -> None:
+                     scratch=None, fused_reduce=None, cluster: bool = False, keep_first: int = 0, sink=None,
+                     gate=None) -> None:
     """Split attention for single tokens: token rows ``rows`` (None: rows
     0..n_tokens-1) each attend their request's context.  Partial results go
     through scratch memory (allocated here unless given) and are reduced into
@@ -1363,7 +1463,9 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
     kernel alone, not inside a decode step (see attention_mma.cu), so the
     engine leaves it off.  Every way adds the splits in split order.
     ``keep_first``: with a window, the first positions of a request that every
-    later query still sees (not with ``cluster``)."""
+    later query still sees (not with ``cluster``).  ``sink``, ``gate``: see
+    ``_sink_and_gate``; they enter where the splits are added up (not with
+    ``cluster``)."""
     if fused_reduce is None:
         fused_reduce = num_splits == 1
     page_size = _check_paged(q, kv_cache, block_table, nkv, d)
@@ -1372,9 +1474,12 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
     _check(out, "out", q.dtype)
     if rows is not None:
         _check(rows, "rows", torch.int32)
+    gate_ld = _sink_and_gate(sink, gate, nh, out.shape[0], q.dtype)
     if cluster:
         if keep_first and window:
             raise KernelError("decode_attention: the cluster form does not keep first tokens")
+        if sink is not None or gate is not None:
+            raise KernelError("decode_attention: the cluster form has neither sink nor gate")
         if not 2 <= num_splits <= 8:
             raise KernelError("decode_attention: a cluster takes 2 to 8 splits")
         _ok(_fn("attention_mma", "rg_decode_attention_cluster")(
@@ -1398,11 +1503,12 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
             counters = _decode_counters[q.device] = torch.zeros(max(need, 4096), dtype=torch.int32, device=q.device)
     else:
         _COUNTER.value += 1                  # the launcher runs two kernels: partial results, then the reduction
-    _ok(_fn("attention_mma", "rg_decode_attention_keep")(
+    _ok(_fn("attention_mma", "rg_decode_attention_sink")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(rows), c_int(n_tokens), _ptr(req_of_token), _ptr(positions), _ptr(part_o), _ptr(part_ml),
         _ptr(counters), c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0),
-        c_int(keep_first if window else 0), c_float(scale), c_int(num_splits), _stream()), "decode_attention")
+        c_int(keep_first if window else 0), c_float(scale), c_int(num_splits), _ptr(sink), _ptr(gate), c_int(gate_ld),
+        _stream()), "decode_attention")
 
 
 _tc_err: dict = {}

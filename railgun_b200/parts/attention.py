@@ -14,7 +14,7 @@ import os
 import torch
 
 from .. import ops
-from ..cache.manager import PagedKVNeed
+from ..cache.manager import PagedKVNeed, StateNeed
 from ..weights.loader import TensorSpec
 from .base import Mixer
 from .latent_attention import rotary_frequencies
@@ -141,21 +141,33 @@ register_mixer("paged_attention", PagedAttention)
 
 class NormedAttention(Mixer):
     """Grouped-query softmax attention with the options that recent designs add to it, each a parameter:
-    biases on the four projections, an RMS norm on every q and k head (one weight vector for all q heads, one
-    for all k heads) before the rotation, rotation of the first ``rot_dims`` numbers of a head in either
-    layout, a learned number per head on the scores (``head_temp``), values of another size than keys, and a
-    sliding window that keeps the request's first ``keep_first`` tokens visible (at their true positions).
+    biases on the four projections, an RMS norm on q and k before the rotation (per head, with one weight vector
+    for all q heads and one for all k heads, or over the whole of q and the whole of k with weights of that
+    size), a short causal convolution per channel on q, k and v directly behind the projections, rotation of
+    the first ``rot_dims`` numbers of a head in either layout, a learned number per head on the scores
+    (``head_temp``), a query factor that grows with the logarithm of the position (``q_temp``), a sink in the
+    softmax's denominator (of score 0, or a learned score per head), a sigmoid gate per head on the heads'
+    outputs, values of another size than keys, and a sliding window that keeps the request's first
+    ``keep_first`` tokens visible (at their true positions).
 
     Keys, queries and values are padded with zeros to one size D (a multiple of 16 that holds both), so the
     key/value pages and the attention kernels are the ordinary ones; the output product's matrix gets zero
-    columns to match.  The score's scale and the head's number are multiplied into q, in 32-bit, before its
-    one rounding.
+    columns to match.  The score's scale, the head's number and the position's factor are multiplied into q, in
+    32-bit, before its one rounding; the sink and the gate are applied where the attention kernels divide by
+    the denominator.
 
     params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_dim``, ``scale`` (None:
     head_dim^-1/2), ``rot_dims``, ``rot_base``, ``rot_layout`` ("interleaved": pairs (2i, 2i + 1), or "half":
     pairs (i, i + rot_dims/2)), ``eps`` (of the q and k norms), ``window`` (0: none), ``keep_first``,
-    ``bias``, ``qk_norm``, ``head_temp`` (booleans, default true), ``base`` (what the tensor names start with
-    after the prefix, default "mix."; the tensors are q, k, v, o, their biases <name>.b, q.norm, k.norm, temp)."""
+    ``bias``, ``head_temp`` (booleans, default true), ``qk_norm`` (true, the default: per head; "whole"; false),
+    ``q_temp`` (None, or (coef, every): q at position p times 1 + coef ln(floor((p + 1) / every) + 1)),
+    ``sink`` (None, "zero" or "learned"), ``out_gate`` (default false), ``conv`` (taps; 0 or 1: none),
+    ``base`` (what the tensor names start with after the prefix, default "mix."; the tensors are q, k, v, o,
+    their biases <name>.b, q.norm, k.norm, temp, sink [heads], g [heads, hidden_size], and q.conv, k.conv,
+    v.conv [channels, taps] with the last column the current token's).
+
+    With a convolution the request keeps, beside its pages, the last taps - 1 projected rows (32-bit) in its
+    state slot."""
 
     @classmethod
     def _base(cls, p, prefix):
@@ -166,6 +178,10 @@ class NormedAttention(Mixer):
         return -(-max(int(p["head_dim"]), int(p["v_dim"])) // 16) * 16
 
     @classmethod
+    def _taps(cls, p) -> int:
+        return max(1, int(p.get("conv") or 1))
+
+    @classmethod
     def tensor_specs(cls, p, prefix):
         W, H, G, d, dv = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"], p["v_dim"]
         b = cls._base(p, prefix)
@@ -174,24 +190,40 @@ class NormedAttention(Mixer):
         if p.get("bias", True):
             out.update({b + "q.b": TensorSpec((H * d,)), b + "k.b": TensorSpec((G * d,)),
                         b + "v.b": TensorSpec((G * dv,)), b + "o.b": TensorSpec((W,))})
-        if p.get("qk_norm", True):
-            out[b + "q.norm"] = TensorSpec((d,), init="norm")
-            out[b + "k.norm"] = TensorSpec((d,), init="norm")
+        norm = p.get("qk_norm", True)
+        if norm:
+            whole = norm == "whole"
+            out[b + "q.norm"] = TensorSpec((H * d if whole else d,), init="norm")
+            out[b + "k.norm"] = TensorSpec((G * d if whole else d,), init="norm")
         if p.get("head_temp", True):
             out[b + "temp"] = TensorSpec((H,), init="norm")
+        if p.get("sink") == "learned":
+            out[b + "sink"] = TensorSpec((H,))
+        if p.get("out_gate"):
+            out[b + "g"] = TensorSpec((H, W))
+        K = cls._taps(p)
+        if K > 1:
+            out.update({b + "q.conv": TensorSpec((H * d, K)), b + "k.conv": TensorSpec((G * d, K)),
+                        b + "v.conv": TensorSpec((G * dv, K))})
         return out
 
     @classmethod
     def cache_need(cls, p):
         window = int(p.get("window") or 0)
-        return PagedKVNeed(int(p["num_kv_heads"]), cls._padded(p), window,
-                           keep_first=int(p.get("keep_first") or 0) if window else 0)
+        pages = PagedKVNeed(int(p["num_kv_heads"]), cls._padded(p), window,
+                            keep_first=int(p.get("keep_first") or 0) if window else 0)
+        K = cls._taps(p)
+        if K == 1:
+            return pages
+        H, G, d, dv = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"]), int(p["v_dim"])
+        return (pages, StateNeed((K - 1, (H + G) * d + G * dv), "float32"))
 
     def __init__(self, p, prefix, env, tensors):
         super().__init__(p, prefix, env, tensors)
         self.H, self.G, self.d, self.dv = (int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"]),
                                            int(p["v_dim"]))
         self.D = self._padded(p)
+        self.C = (self.H + self.G) * self.d + self.G * self.dv
         if self.H % self.G:
             raise ValueError(f"{self.H} heads cannot share {self.G} key/value heads")
         if self.D > 256:
@@ -208,12 +240,17 @@ class NormedAttention(Mixer):
         self.eps = float(p.get("eps") or 0.0)
         scale = float(p["scale"]) if p.get("scale") is not None else float(self.d) ** -0.5
         b = self._base(p, prefix)
-        self.w_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in ("q", "k", "v")], dim=0).contiguous()
+        names = ["q", "k", "v"] + (["g"] if p.get("out_gate") else [])
+        self.out_gate = bool(p.get("out_gate"))
+        self.w_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in names], dim=0).contiguous()
         self.b_qkv = self.b_o = None
         if p.get("bias", True):
-            self.b_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in ("q.b", "k.b", "v.b")], dim=0).contiguous()
+            biases = [tensors.get(b + n, env.dtype) for n in ("q.b", "k.b", "v.b")]
+            if self.out_gate:                                        # the gate's rows of the product have no bias
+                biases.append(torch.zeros(self.H, dtype=env.dtype, device=biases[0].device))
+            self.b_qkv = torch.cat(biases, dim=0).contiguous()
             self.b_o = tensors.get(b + "o.b", env.dtype).contiguous()
-        tensors.drop(b + "q", b + "k", b + "v", b + "q.b", b + "k.b", b + "v.b")
+        tensors.drop(b + "q", b + "k", b + "v", b + "g", b + "q.b", b + "k.b", b + "v.b")
         w_o = tensors.get(b + "o", env.dtype)
         if self.D != self.dv:
             # zero columns where the attention's output rows carry padding
@@ -223,34 +260,64 @@ class NormedAttention(Mixer):
             tensors.drop(b + "o")
         self.w_o = w_o.contiguous()
         norm = p.get("qk_norm", True)
+        if norm not in (True, False, None, "whole", "head"):
+            raise ValueError(f"qk_norm {norm!r} is not known; known: true (per head), 'whole', false")
+        self.norm_whole = norm == "whole"
         self.q_norm = tensors.get(b + "q.norm", torch.float32).contiguous() if norm else None
         self.k_norm = tensors.get(b + "k.norm", torch.float32).contiguous() if norm else None
         # what every q head is multiplied by: the score's scale times the head's own number
         self.factor = torch.full((self.H,), scale, dtype=torch.float32, device=env.device)
         if p.get("head_temp", True):
             self.factor = (self.factor * tensors.get(b + "temp", torch.float32)).contiguous()
+        temp = p.get("q_temp")
+        self.temp_coef, self.temp_every = (float(temp[0]), int(temp[1])) if temp else (0.0, 0)
+        if self.temp_every < 0:
+            raise ValueError(f"q_temp.every {self.temp_every} must be positive")
+        sink = p.get("sink")
+        if sink not in (None, "zero", "learned"):
+            raise ValueError(f"sink {sink!r} is not known; known: None, 'zero', 'learned'")
+        self.sink = None
+        if sink == "zero":
+            self.sink = torch.zeros(self.H, dtype=torch.float32, device=env.device)
+        elif sink == "learned":
+            self.sink = tensors.get(b + "sink", torch.float32).contiguous()
+        self.K = self._taps(p)
+        self.taps = None
+        if self.K > 1:
+            self.taps = torch.cat([tensors.get(b + n, torch.float32) for n in ("q.conv", "k.conv", "v.conv")],
+                                  dim=0).t().contiguous()                                  # [taps, channels]
         base = float(p.get("rot_base") or 10000.0)
         self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
                                         lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
 
     def forward(self, x, batch, cache, writes=True):
-        H, G, d, dv, D = self.H, self.G, self.d, self.dv, self.D
-        qkv = ops.linear(x, self.w_qkv, bias=self.b_qkv)
-        slots = batch.slot_mapping[cache.group] if writes else None
-        q = ops.attention_prepare(qkv, cache.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
-                                  self.interleaved, batch.positions, slots, self.factor, H, G, d, dv, D)
-        out = self.attend(q.view(-1, H * D), batch, cache)
+        H, G, d, dv, D, C = self.H, self.G, self.d, self.dv, self.D, self.C
+        proj = ops.linear(x, self.w_qkv, bias=self.b_qkv)                     # [T, q | k | v (| gate)]
+        pages = cache.parts[0] if self.K > 1 else cache
+        qkv = proj if proj.shape[1] == C else proj[:, :C]
+        if self.K > 1:
+            state = cache.parts[1].state
+            qkv = ops.causal_conv(proj, 0, self.taps, state, batch, torch.float32)
+            if writes:
+                ops.conv_state_update(proj, 0, state, batch)
+        slots = batch.slot_mapping[pages.group] if writes else None
+        q = ops.attention_prepare(qkv, pages.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
+                                  self.interleaved, batch.positions, slots, self.factor, H, G, d, dv, D,
+                                  norm_whole=self.norm_whole, temp_coef=self.temp_coef, temp_every=self.temp_every,
+                                  out_dtype=self.env.dtype)
+        gate = proj[:, C:] if self.out_gate else None
+        out = self.attend(q.view(-1, H * D), batch, pages, gate)
         return ops.linear(out, self.w_o, bias=self.b_o)
 
-    def attend(self, q, batch, cache):
+    def attend(self, q, batch, cache, gate=None):
         """bfloat16 runs on the tensor cores (requests with several tokens through the flash-style kernel, single
-        tokens through the split kernel; both know the window and the kept first tokens); the 32-bit path runs the
-        general kernel."""
+        tokens through the split kernel; both know the window, the kept first tokens, the sink and the gate); the
+        32-bit path runs the general kernel."""
         H, G, D = self.H, self.G, self.D
         table = batch.block_table[cache.group]
         if q.dtype != torch.bfloat16:
             return ops.paged_attention_general(q, q.shape[1], cache.kv, table, batch.req_of_token, batch.positions,
-                                               H, G, D, self.window, 1.0, self.keep_first)
+                                               H, G, D, self.window, 1.0, self.keep_first, sink=self.sink, gate=gate)
         out = torch.empty((q.shape[0], H * D), dtype=q.dtype, device=q.device)
         kv_tiles = G * (-(-(H // G) // 8))
         reach = batch.max_context_len
@@ -258,12 +325,13 @@ class NormedAttention(Mixer):
             reach = min(reach, self.window + self.keep_first)
         if batch.num_prefill_tiles:
             ops.prefill_attention(q, q.shape[1], out, cache.kv, table, batch.prefill_tiles, batch.positions,
-                                  H, G, D, self.window, 1.0, self.keep_first)
+                                  H, G, D, self.window, 1.0, self.keep_first, sink=self.sink, gate=gate)
         n = batch.num_tokens if batch.decode_only else batch.num_decode_rows
         if n:
             ops.decode_attention(q, q.shape[1], out, cache.kv, table, None if batch.decode_only else batch.decode_rows,
                                  n, batch.req_of_token, batch.positions, H, G, D, self.window, 1.0,
-                                 ops.decode_splits(n, kv_tiles, reach), keep_first=self.keep_first)
+                                 ops.decode_splits(n, kv_tiles, reach), keep_first=self.keep_first, sink=self.sink,
+                                 gate=gate)
         return out
 
 

@@ -26,7 +26,9 @@ through a norm of its own, and their outputs are added to it together:
 x = x + (mixer(norm1(x)) + ffn(norm2(x))).  The sum of the branches' outputs,
 its addition to the 32-bit residual and the next layer's norms are one
 kernel (ops.PendingSum, ops.add_group_rmsnorm): the norms of one layer differ
-in their weights only, so the row's statistics are computed once.
+in their weights only, so the row's statistics are computed once.  Branches
+that are given the SAME norm (the same tensor with the same constants) read
+one normed row: h = norm(x); x = x + (mixer(h) + ffn(h)).
 
 "reinject" (a stream operation): x <- W [x; x0] with x0 the embedding's
 output, for models that feed the input again at the start of a pass over a
@@ -77,8 +79,12 @@ class ParallelResidual(Arrangement):
         if isinstance(pending, (ops.PendingLinear, ops.PendingNormed)):
             pending = pending.materialize()
         if same:
-            hs = ops.add_group_rmsnorm(stream.resid, pending, [n.weight for n in norms], norms[0].groups, norms[0].eps,
-                                       norms[0].env.dtype)
+            # branches behind one and the same norm share its output
+            shared = len(norms) == 2 and norms[0].prefix == norms[1].prefix and norms[0].params == norms[1].params
+            hs = ops.add_group_rmsnorm(stream.resid, pending, [n.weight for n in (norms[:1] if shared else norms)],
+                                       norms[0].groups, norms[0].eps, norms[0].env.dtype)
+            if shared:
+                hs = [hs[0], hs[0]]
         else:
             # norms of different kinds: the first one adds what is pending, the others read the sum
             hs = []

@@ -21,7 +21,8 @@ class RMSNorm(Norm):
     multiplies the normed value) and ``mult`` (a constant that does): both are
     multiplied into the weight at load, in 32-bit; ``groups`` (default 1): the
     row is cut into that many equal consecutive parts and each part is divided
-    by its own root mean square."""
+    by its own root mean square; ``one_plus`` (default false): the stored
+    weight sits around zero and the normed value is multiplied by 1 + w."""
 
     @classmethod
     def tensor_specs(cls, params, prefix):
@@ -34,6 +35,8 @@ class RMSNorm(Norm):
         super().__init__(params, prefix, env, tensors)
         self.eps = float(params["eps"])
         self.weight = tensors.get(prefix + params["name"], torch.float32)
+        if params.get("one_plus"):
+            self.weight = self.weight + 1.0
         if params.get("scale_name"):
             self.weight = self.weight * tensors.get(prefix + params["scale_name"], torch.float32)
         if params.get("mult") is not None and float(params["mult"]) != 1.0:

@@ -10,34 +10,72 @@ into one buffer, already multiplied by their constants in 32-bit before the
 one rounding, and ONE product with the output matrices side by side gives
 sum_b c_b W_o,b z_b.  What the branches keep between steps is asked for as a
 tuple of needs, one per branch.
+
+With ``out_norms`` every branch's output is RMS-normed over the width with a
+weight of its own before the sum, sum_b c_b norm_b(branch_b(x)): the branches
+are then any mixers, run one after the other through their ``forward``, and
+the norms, constants and sum are one kernel (ops.norm_sum, 32-bit).
 """
 from __future__ import annotations
 
 import torch
 
 from .. import ops
-from .base import Mixer
+from ..weights.loader import TensorSpec
+from .base import CacheView, Mixer
 from .registry import MIXERS, register_mixer
 
 
 class Parallel(Mixer):
-    """params: ``branches``: ((PartSpec of a mixer, constant), ...)."""
+    """params: ``branches``: ((PartSpec of a mixer, constant), ...).  Optional ``out_norms``: one tensor name
+    (after the prefix, [hidden_size], a plain weight) per branch, with ``hidden_size`` and ``eps``."""
 
     @classmethod
     def tensor_specs(cls, p, prefix):
         out = {}
         for spec, _ in p["branches"]:
             out.update(MIXERS.get(spec.kind).tensor_specs(spec.params, prefix))
+        for name in p.get("out_norms") or ():
+            out[prefix + name] = TensorSpec((int(p["hidden_size"]),), init="norm")
+        return out
+
+    @classmethod
+    def _branch_needs(cls, p):
+        """Per branch: (its needs as a tuple, whether it asked for a tuple itself)."""
+        out = []
+        for spec, _ in p["branches"]:
+            need = MIXERS.get(spec.kind).cache_need(spec.params)
+            out.append((tuple(need), True) if isinstance(need, (tuple, list)) else ((need,), False))
         return out
 
     @classmethod
     def cache_need(cls, p):
-        return tuple(MIXERS.get(spec.kind).cache_need(spec.params) for spec, _ in p["branches"])
+        # one flat tuple: a branch that keeps several things itself gets that many places in a row
+        return tuple(n for needs, _ in cls._branch_needs(p) for n in needs)
+
+    def _views(self, cache):
+        """The branches' cache views out of this mixer's: a branch that asked for a tuple of needs sees a view with
+        one part per need, as it would alone."""
+        views, at = [], 0
+        for needs, composite in self._needs:
+            views.append(CacheView(cache.cache_id, parts=cache.parts[at:at + len(needs)]) if composite
+                         else cache.parts[at])
+            at += len(needs)
+        return views
 
     def __init__(self, p, prefix, env, tensors):
         super().__init__(p, prefix, env, tensors)
         self.parts = [MIXERS.get(spec.kind)(spec.params, prefix, env, tensors) for spec, _ in p["branches"]]
         self.scales = [float(c) for _, c in p["branches"]]
+        self._needs = self._branch_needs(p)
+        self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts)
+        self.out_norms = None
+        if p.get("out_norms"):
+            if len(p["out_norms"]) != len(self.parts) or len(self.parts) > 4:
+                raise ValueError("'parallel' with out_norms: one norm per branch, four branches at most")
+            self.out_norms = [tensors.get(prefix + n, torch.float32).contiguous() for n in p["out_norms"]]
+            self.eps = float(p["eps"])
+            return
         for part in self.parts:
             if not all(hasattr(part, a) for a in ("mix", "w_o", "w_in")):
                 raise ValueError(f"{type(part).__name__} cannot be a branch of 'parallel': it has no mix(), w_in and w_o")
@@ -58,11 +96,14 @@ class Parallel(Mixer):
         self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts)
 
     def forward(self, x, batch, cache, writes=True):
+        if self.out_norms is not None:
+            ys = [part.forward(x, batch, view, writes) for part, view in zip(self.parts, self._views(cache))]
+            return ops.norm_sum(ys, self.out_norms, self.scales, self.eps)
         T = x.shape[0]
         proj = ops.linear(x, self.w_in)
         z = torch.empty((T, sum(self.widths)), dtype=self.env.dtype, device=self.w_o.device)
         off = at = 0
-        for part, c, n, n_in, view in zip(self.parts, self.scales, self.widths, self.in_widths, cache.parts):
+        for part, c, n, n_in, view in zip(self.parts, self.scales, self.widths, self.in_widths, self._views(cache)):
             part.mix(x, batch, view, writes, out=z[:, off:off + n], out_scale=c, proj=proj[:, at:at + n_in])
             off += n
             at += n_in

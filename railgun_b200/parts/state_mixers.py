@@ -44,14 +44,20 @@ def _base(p, prefix):
 class Retention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``head_dim``, ``v_dim``, ``decay`` (one number per head),
     ``rot_dims``, ``rot_base``, ``eps`` (of the heads' norm), ``k_scale`` (None: head_dim^-1/2), ``base`` (what
-    the tensor names start with after the prefix, default "mix."; the tensors are q, k, v, g, o)."""
+    the tensor names start with after the prefix, default "mix."; the tensors are q, k, v, g, o).  Optional:
+    ``activation`` "silu" (on q, k and v, as lightning attention has it; default none), ``norm`` "whole" (one
+    root mean square over all heads' outputs with the weight tensor ``norm`` [heads * v_dim]; default "head":
+    every head by its own, no weight), ``gate`` "sigmoid" (default "silu")."""
 
     @classmethod
     def tensor_specs(cls, p, prefix):
         W, H, d, dv = p["hidden_size"], p["num_heads"], p["head_dim"], p["v_dim"]
         b = _base(p, prefix)
-        return {b + "q": TensorSpec((H * d, W)), b + "k": TensorSpec((H * d, W)), b + "v": TensorSpec((H * dv, W)),
-                b + "g": TensorSpec((H * dv, W)), b + "o": TensorSpec((W, H * dv))}
+        out = {b + "q": TensorSpec((H * d, W)), b + "k": TensorSpec((H * d, W)), b + "v": TensorSpec((H * dv, W)),
+               b + "g": TensorSpec((H * dv, W)), b + "o": TensorSpec((W, H * dv))}
+        if p.get("norm") == "whole":
+            out[b + "norm"] = TensorSpec((H * dv,), init="norm")
+        return out
 
     @classmethod
     def cache_need(cls, p):
@@ -69,10 +75,15 @@ class Retention(Mixer):
             raise ValueError(f"{self.rot_dims} rotated numbers do not fit a head of {self.d}")
         self.eps = float(p.get("eps") or 0.0)
         self.k_scale = float(p["k_scale"]) if p.get("k_scale") is not None else float(self.d) ** -0.5
+        act, norm, gate = p.get("activation"), p.get("norm") or "head", p.get("gate") or "silu"
+        if act not in (None, "silu") or norm not in ("head", "whole") or gate not in ops.HEAD_GATES:
+            raise ValueError(f"retention: activation {act!r}, norm {norm!r} or gate {gate!r} is not known")
+        self.silu, self.whole, self.gate = act == "silu", norm == "whole", gate
         b = _base(p, prefix)
         self.w_in = torch.cat([tensors.get(b + n, env.dtype) for n in ("q", "k", "v", "g")], dim=0).contiguous()
         tensors.drop(b + "q", b + "k", b + "v", b + "g")
         self.w_o = tensors.get(b + "o", env.dtype)
+        self.norm = tensors.get(b + "norm", torch.float32).contiguous() if self.whole else None
         base = float(p.get("rot_base") or 10000.0)
         self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
                                         lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
@@ -80,10 +91,15 @@ class Retention(Mixer):
     def forward(self, x, batch, cache, writes=True):
         H, d, dv = self.H, self.d, self.dv
         proj = ops.linear(x, self.w_in)                                      # [T, q | k | v | gate]
-        q, k = ops.retention_prepare(proj, 0, H * d, self.freq, self.rot_dims, batch.positions, H, d, self.k_scale)
-        o = ops.state_scan(q.view(-1, H * d), k.view(-1, H * d), proj[:, 2 * H * d:2 * H * d + H * dv], cache.state,
-                           batch, H, d, dv, decay=self.decay)
-        z = ops.head_norm_gate(o, proj[:, 2 * H * d + H * dv:], None, self.eps, self.env.dtype)
+        if self.silu:
+            q, k, v = ops.retention_prepare(proj, 0, H * d, self.freq, self.rot_dims, batch.positions, H, d,
+                                            self.k_scale, silu=True, v_off=2 * H * d, dv=dv)
+        else:
+            q, k = ops.retention_prepare(proj, 0, H * d, self.freq, self.rot_dims, batch.positions, H, d, self.k_scale)
+            v = proj[:, 2 * H * d:2 * H * d + H * dv]
+        o = ops.state_scan(q.view(-1, H * d), k.view(-1, H * d), v, cache.state, batch, H, d, dv, decay=self.decay)
+        z = ops.head_norm_gate(o, proj[:, 2 * H * d + H * dv:], self.norm, self.eps, self.env.dtype, whole=self.whole,
+                               gate_kind=self.gate)
         return ops.linear(z, self.w_o)
 
 
