@@ -67,7 +67,7 @@ class ConvAttentionConfig:
     dim: int
     vdim: int
     scale: float
-    conv: int               # taps of the convolutions (1: the current token only)
+    conv: int               # taps of the convolutions (1: a factor per channel on the current token; 0: none)
     rot_dims: int
     rot_base: float
 
@@ -81,12 +81,13 @@ class ConvAttentionConfig:
         if dims % 2 or dims > dim:
             raise ConfigError(f"{r.where}: rot.dims {dims} must be even and at most dim {dim}")
         return ConvAttentionConfig(heads=heads, kv_heads=kv, dim=dim, vdim=r.integer("vdim", minimum=1),
-                                   scale=r.number("scale", positive=True), conv=r.integer("conv", 1, minimum=1),
+                                   scale=r.number("scale", positive=True), conv=r.integer("conv", 0, minimum=0),
                                    rot_dims=dims, rot_base=base)
 
     def to_dict(self) -> dict:
-        d = dict(conv=self.conv, dim=self.dim, heads=self.heads, kv_heads=self.kv_heads, scale=self.scale,
-                 vdim=self.vdim)
+        d = dict(dim=self.dim, heads=self.heads, kv_heads=self.kv_heads, scale=self.scale, vdim=self.vdim)
+        if self.conv:
+            d["conv"] = self.conv
         if self.rot_dims:
             d["rot"] = dict(base=self.rot_base, dims=self.rot_dims)
         return d

@@ -76,10 +76,12 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
         float* s = base + (size_t)j * 2 * N;
         float* c = s + N;
         if (scoring == 1) {
+            // without a correction the largest scores are the largest logits, which do not saturate
             for (int n = lane; n < N; n += 32) {
-                const float p = 1.f / (1.f + expf(-s[n]));
+                const float z = s[n];
+                const float p = 1.f / (1.f + expf(-z));
                 s[n] = p;
-                c[n] = p + (correction ? correction[n] : 0.f);
+                c[n] = correction ? p + correction[n] : z;
             }
         } else {
             float mx = -INFINITY;

@@ -161,7 +161,8 @@ class NormedAttention(Mixer):
     pairs (i, i + rot_dims/2)), ``eps`` (of the q and k norms), ``window`` (0: none), ``keep_first``,
     ``bias``, ``head_temp`` (booleans, default true), ``qk_norm`` (true, the default: per head; "whole"; false),
     ``q_temp`` (None, or (coef, every): q at position p times 1 + coef ln(floor((p + 1) / every) + 1)),
-    ``sink`` (None, "zero" or "learned"), ``out_gate`` (default false), ``conv`` (taps; 0 or 1: none),
+    ``sink`` (None, "zero" or "learned"), ``out_gate`` (default false), ``conv`` (taps; 0: none; 1: a factor per
+    channel),
     ``base`` (what the tensor names start with after the prefix, default "mix."; the tensors are q, k, v, o,
     their biases <name>.b, q.norm, k.norm, temp, sink [heads], g [heads, hidden_size], and q.conv, k.conv,
     v.conv [channels, taps] with the last column the current token's).
@@ -179,7 +180,7 @@ class NormedAttention(Mixer):
 
     @classmethod
     def _taps(cls, p) -> int:
-        return max(1, int(p.get("conv") or 1))
+        return max(0, int(p.get("conv") or 0))
 
     @classmethod
     def tensor_specs(cls, p, prefix):
@@ -202,7 +203,7 @@ class NormedAttention(Mixer):
         if p.get("out_gate"):
             out[b + "g"] = TensorSpec((H, W))
         K = cls._taps(p)
-        if K > 1:
+        if K >= 1:
             out.update({b + "q.conv": TensorSpec((H * d, K)), b + "k.conv": TensorSpec((G * d, K)),
                         b + "v.conv": TensorSpec((G * dv, K))})
         return out
@@ -213,7 +214,7 @@ class NormedAttention(Mixer):
         pages = PagedKVNeed(int(p["num_kv_heads"]), cls._padded(p), window,
                             keep_first=int(p.get("keep_first") or 0) if window else 0)
         K = cls._taps(p)
-        if K == 1:
+        if K <= 1:
             return pages
         H, G, d, dv = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"]), int(p["v_dim"])
         return (pages, StateNeed((K - 1, (H + G) * d + G * dv), "float32"))
@@ -283,7 +284,7 @@ class NormedAttention(Mixer):
             self.sink = tensors.get(b + "sink", torch.float32).contiguous()
         self.K = self._taps(p)
         self.taps = None
-        if self.K > 1:
+        if self.K >= 1:
             self.taps = torch.cat([tensors.get(b + n, torch.float32) for n in ("q.conv", "k.conv", "v.conv")],
                                   dim=0).t().contiguous()                                  # [taps, channels]
         base = float(p.get("rot_base") or 10000.0)
@@ -295,10 +296,10 @@ class NormedAttention(Mixer):
         proj = ops.linear(x, self.w_qkv, bias=self.b_qkv)                     # [T, q | k | v (| gate)]
         pages = cache.parts[0] if self.K > 1 else cache
         qkv = proj if proj.shape[1] == C else proj[:, :C]
-        if self.K > 1:
-            state = cache.parts[1].state
-            qkv = ops.causal_conv(proj, 0, self.taps, state, batch, torch.float32)
-            if writes:
+        if self.K >= 1:
+            state = cache.parts[1].state if self.K > 1 else None
+            qkv = ops.causal_conv(qkv, 0, self.taps, state, batch, torch.float32)
+            if writes and state is not None:
                 ops.conv_state_update(proj, 0, state, batch)
         slots = batch.slot_mapping[pages.group] if writes else None
         q = ops.attention_prepare(qkv, pages.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,

@@ -114,7 +114,8 @@ def gated_attention(h, w, p, m, pos):
     q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, d)
     k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, d)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
-    q = q * query_temperature(pos, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
+    if m.get("q_temp"):
+        q = q * query_temperature(pos, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
     o = sink_softmax_attention(q, k, v, m["scale"], np.zeros(H))
     o = o * sigmoid(h @ w[p + "g"].T)[:, :, None]
     return o.reshape(T, H * dv) @ w[p + "o"].T + w[p + "o.b"]
@@ -125,9 +126,9 @@ def conv_attention(h, w, p, m, pos, eps):
     and of k, interleaved rotation of part of each head, softmax with a learned sink per head."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = causal_conv(h @ w[p + "q"].T, w[p + "q.conv"])
-    k = causal_conv(h @ w[p + "k"].T, w[p + "k.conv"])
-    v = causal_conv(h @ w[p + "v"].T, w[p + "v.conv"])
+    q, k, v = h @ w[p + "q"].T, h @ w[p + "k"].T, h @ w[p + "v"].T
+    if m.get("conv"):
+        q, k, v = causal_conv(q, w[p + "q.conv"]), causal_conv(k, w[p + "k.conv"]), causal_conv(v, w[p + "v.conv"])
     q = plain_norm(q, w[p + "q.norm"], eps).reshape(T, H, d)
     k = plain_norm(k, w[p + "k.norm"], eps).reshape(T, G, d)
     rot = m.get("rot")
@@ -174,17 +175,21 @@ def dense_ff(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def router_choice(h, w, p, f):
-    """(chosen experts [T, top], their weights [T, top]): sigmoid scores, the largest, as they are."""
-    s = sigmoid(h @ w[p + "router"].T)
+def router_choice(h, w, p, f, margins=None):
+    """(chosen experts [T, top], their weights [T, top]): sigmoid scores, the largest, as they are.  ``margins``
+    (a list) receives, per token, how far the last chosen logit is above the first one that is not."""
+    z = h @ w[p + "router"].T
     top = f["router"]["top"]
-    ids = np.argsort(-s, axis=1, kind="stable")[:, :top]
-    return ids, np.take_along_axis(s, ids, axis=1)
+    ids = np.argsort(-z, axis=1, kind="stable")[:, :top]                      # the sigmoid keeps the order
+    if margins is not None:
+        zs = -np.sort(-z, axis=1)
+        margins.append(zs[:, top - 1] - zs[:, top] if top < z.shape[1] else np.full(len(z), np.inf))
+    return ids, sigmoid(np.take_along_axis(z, ids, axis=1))
 
 
-def expert_ff(h, w, p, f):
+def expert_ff(h, w, p, f, margins=None):
     """Each chosen expert reads its weight times h: sum_e down_e relu(up_e (s_e h))^2."""
-    ids, wt = router_choice(h, w, p, f)
+    ids, wt = router_choice(h, w, p, f, margins)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(ids[t], wt[t]):
@@ -194,7 +199,7 @@ def expert_ff(h, w, p, f):
 
 
 # ---- the model -------------------------------------------------------------------------------------------
-def layer_forward(x, w, cfg, i, pos):
+def layer_forward(x, w, cfg, i, pos, margins=None):
     L = cfg["layers"][i]
     eps = cfg["norm"]["eps"]
     p = f"l{i}."
@@ -207,18 +212,19 @@ def layer_forward(x, w, cfg, i, pos):
         raise ValueError(L["type"])
     f = L.get("mlp")
     if f is not None:
-        y = y + (dense_ff(h, w, p + "mlp.") if f["kind"] == "dense" else expert_ff(h, w, p + "mlp.", f))
+        y = y + (dense_ff(h, w, p + "mlp.") if f["kind"] == "dense" else expert_ff(h, w, p + "mlp.", f, margins))
     return x + y
 
 
-def forward(tokens, w, cfg, return_layers=False):
-    """Logits [T, vocab] of one sequence from position 0 (and the stream after every layer)."""
+def forward(tokens, w, cfg, return_layers=False, margins=None):
+    """Logits [T, vocab] of one sequence from position 0 (and the stream after every layer).  ``margins`` (a list)
+    receives one array [T] per layer with experts: the routers' margins."""
     tokens = np.asarray(tokens)
     pos = np.arange(len(tokens))
     x = w["embed"][tokens]
     layers = []
     for i in range(len(cfg["layers"])):
-        x = layer_forward(x, w, cfg, i, pos)
+        x = layer_forward(x, w, cfg, i, pos, margins)
         layers.append(x)
     logits = (one_plus_norm(x, w["final.norm"], cfg["norm"]["eps"]) @ w["embed"].T) * cfg["logit_scale"]
     return (logits, np.stack(layers)) if return_layers else logits
