@@ -770,6 +770,137 @@ def run_mepatar(args):
     return 0
 
 
+def kasarax_sizes(name):
+    """(Kasarax configuration, the Mepatar configuration of equal width, layers and vocabulary beside it)."""
+    def kas(width, heads, kv, d, ff, experts, top, eff, vocab):
+        att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=d, vdim=d, scale=d ** -0.5,
+                                                q_temp=dict(coef=0.1, every=256)))
+        left = dict(heads=heads // 2, kv_heads=kv, dim=d, vdim=d, conv=4, scale=d ** -0.5, rot=dict(base=10000.0, dims=d // 2))
+        right = dict(heads=heads // 2, dim=d, vdim=d, decay=[1.0 - 2.0 ** (-5 - 0.4 * i) for i in range(heads // 2)])
+        par = dict(type="parallel", mixer=dict(left=left, right=right))
+        dense = dict(kind="dense", ff=ff)
+        moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=eff))
+        layers = [dict(att, mlp=dense), dict(par, mlp=moe), dict(par, mlp=dense), dict(att, mlp=moe), dict(par, mlp=moe),
+                  dict(par, mlp=dense)]
+        return dict(architecture="Kasarax", width=width, vocab=vocab, norm=dict(eps=1e-6), logit_scale=0.5, layers=layers)
+
+    if name == "w2048":      # 16 heads of 128 (2 key/value heads), halves of 8 heads; 32 experts of 2,048, 4 chosen
+        return kas(2048, 16, 2, 128, 8192, 32, 4, 2048, 32768), mepatar_sizes(name)[0]
+    if name == "w1024":      # 8 heads of 128 (2 key/value heads), halves of 4 heads; 16 experts of 1,024, 4 chosen
+        return kas(1024, 8, 2, 128, 4096, 16, 4, 1024, 32768), mepatar_sizes(name)[0]
+    raise ValueError(name)
+
+
+def kasarax_decode_bytes(cfg, batch, context):
+    """Bytes a decode step has to read or write: the weights of every layer (of the experts, those that `batch`
+    tokens can reach at most), the head, and what the live requests keep: the attention caches as far back as the
+    context, the lightning states in 32-bit (read and written) and the convolutions' tails."""
+    W, V = cfg["width"], cfg["vocab"]
+    total = V * W * 2
+
+    def attention(m, bias):
+        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        D = -(-max(d, dv) // 16) * 16
+        return ((H + G) * d + G * dv + (H if bias else 0)) * W * 2 + W * H * dv * 2 + batch * context * G * 2 * D * 2
+
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            total += attention(m, True)
+        else:
+            a, r = m["left"], m["right"]
+            total += attention(a, False)
+            total += batch * (a.get("conv", 1) - 1) * ((a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"]) * 4 * 2
+            H, d, dv = r["heads"], r["dim"], r["vdim"]
+            total += (2 * H * d + 2 * H * dv) * W * 2 + W * H * dv * 2 + batch * H * d * dv * 4 * 2
+        f = L["mlp"]
+        if f and f["kind"] == "dense":
+            total += 3 * f["ff"] * W * 2
+        elif f:
+            r, e = f["router"], f["expert"]
+            total += r["experts"] * W * 4 + min(r["experts"], batch * r["top"]) * 2 * e["ff"] * W * 2
+    return total
+
+
+def kasarax_prefill_flops(cfg, T):
+    """FLOPs of one prompt of T tokens by the design's own arithmetic: products, the chosen experts, causal
+    attention, and the lightning states' updates and read-outs (4 d dv per head and token)."""
+    W, V = cfg["width"], cfg["vocab"]
+    total = 2 * V * W
+    pairs = T * (T + 1) // 2
+
+    def attention(m, gate):
+        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        return 2 * T * (((H + G) * d + G * dv + (H if gate else 0)) * W + W * H * dv) + H * 2 * (d + dv) * pairs
+
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            total += attention(m, True)
+        else:
+            r = m["right"]
+            H, d, dv = r["heads"], r["dim"], r["vdim"]
+            total += attention(m["left"], False) + 2 * T * ((2 * H * d + 2 * H * dv) * W + W * H * dv) + T * H * 4 * d * dv
+        f = L["mlp"]
+        if f and f["kind"] == "dense":
+            total += 2 * T * 3 * f["ff"] * W
+        elif f:
+            total += 2 * T * (f["router"]["experts"] * W + f["router"]["top"] * 2 * f["expert"]["ff"] * W)
+    return total
+
+
+def run_kasarax(args):
+    """Prefill and decode throughput of Kasarax at layer sizes of real models (random weights), beside Mepatar
+    (the framework's closest design: a mixer and a feed-forward side by side on one stream, attention and matrix
+    states, routed experts) at equal width, number of layers and vocabulary.  One JSON line per model and size."""
+    import numpy as np
+    import torch
+    from railgun_b200.engine.batch import StepEntry
+    from railgun_b200.engine.engine import Engine
+    page, pool_tokens = 16, 64 * 4096
+    pk, pk_src = peaks()
+    for size in (args.sizes.split(",") if args.sizes else ["w1024", "w2048"]):
+        for label, cfg in zip(("kasarax", "mepatar"), kasarax_sizes(size)):
+            mdir = model_folder(cfg)
+            eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
+                         max_num_batched_tokens=8192, max_model_len=4096)
+            runner = eng.runner
+            V = cfg["vocab"]
+            rng = np.random.default_rng(0)
+            _, _, time_decode = decode_tools(runner, V, rng)
+            line = {"mode": "kasarax", "size": size, "model": label, "layer_runs": len(runner.model.order),
+                    "cache_bytes_per_token": runner.cache.bytes_per_token()}
+            for b in (8, 64):
+                tok_s, ms, n_launch, _ = time_decode(b, args.steps, args.warmup, 1000 * b, args.context)
+                line[f"decode_b{b}_tok_s"], line[f"decode_b{b}_ms"] = round(tok_s, 1), round(ms, 4)
+                line[f"decode_b{b}_launches_per_step"] = n_launch // args.steps
+                ctx = args.context + args.warmup + args.steps // 2
+                by = kasarax_decode_bytes(cfg, b, ctx) if label == "kasarax" else mepatar_decode_bytes(cfg, b, ctx)
+                line[f"decode_b{b}_GB_per_step"] = round(by / 1e9, 3)
+                line[f"decode_b{b}_frac_hbm"] = round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
+            prompt = rng.integers(0, V, size=args.tokens).tolist()
+            times = []
+            for i in range(args.warmup + 7):
+                torch.cuda.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                runner.step([StepEntry(7000 + i, prompt, [args.tokens - 1])])
+                t1.record()
+                torch.cuda.synchronize()
+                runner.end([7000 + i])
+                times.append(t0.elapsed_time(t1))
+            runner.check_device_errors()
+            ms = sorted(times[args.warmup:])[len(times[args.warmup:]) // 2]
+            fl = kasarax_prefill_flops(cfg, args.tokens) if label == "kasarax" else mepatar_prefill_flops(cfg, args.tokens)
+            line.update(prefill_tokens=args.tokens, prefill_ms=round(ms, 3), prefill_tok_s=round(args.tokens / ms * 1e3, 1),
+                        prefill_TFLOP=round(fl / 1e12, 3), prefill_frac_flops=round(fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                        peaks=pk_src)
+            print(json.dumps(line), flush=True)
+            del eng, runner, time_decode
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_kernels(args):
     """Times the hot kernels one by one, each as a CUDA graph of 16 calls over 16 different operand sets (so
     that weights and caches come from HBM, not L2), with CUDA events around replays.  One JSON line per case."""
@@ -1135,6 +1266,119 @@ def run_kernels(args):
                 **({"frac_hbm": round(by / res[4] / 1e3 / pk["hbm_gbs"], 3), "plain_window_frac_hbm": round(
                     (B * 512 * G * 2 * dd * 2) / res[0] / 1e3 / pk["hbm_gbs"], 3)} if B > 1 else
                    {"frac_flops": round(fl / res[4] / 1e6 / pk["bf16_tflops"], 3)}))
+    if on("kasarax_rows"):
+        # Kasarax's own kernels by the bytes they have to move, each beside the like kernel of another design: the sum
+        # of two normed branches beside the norm in groups, the per-token work before attention with norms over the
+        # whole of q and k beside the per-head norms, attention with a sink and a gate per head beside the same
+        # kernels without, the norm over all lightning heads beside the per-head norm, the experts' rows times
+        # their weights beside the plain gather
+        from types import SimpleNamespace
+        pk, _ = peaks()
+        W, Hh, dd, G, K = 2048, 16, 128, 2, 4
+        Hl = Hh // 2
+        from railgun_b200.parts.latent_attention import rotary_frequencies
+        freq = rotary_frequencies(dd // 2, 10000.0).to(dev)
+        for T in (64, 4096):
+            R_ = 1 if T > 64 else T
+            per = T // R_
+            batch = SimpleNamespace(cu_seqlens=torch.arange(0, T + 1, per, dtype=torch.int32, device=dev),
+                                    num_requests=R_, req_of_token=(torch.arange(T, device=dev) // per).to(torch.int32),
+                                    start_pos=torch.full((R_,), 1000, dtype=torch.int32, device=dev),
+                                    state_slots=torch.arange(R_, dtype=torch.int32, device=dev), max_query_len=per,
+                                    positions=(1000 + torch.arange(T, device=dev) % per).to(torch.int32))
+            ya = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(L)]
+            yb = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(L)]
+            rs = [torch.randn(T, W, device=dev) for _ in range(L)]
+            nw, nw2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+            us = timed(lambda: [ops.norm_sum([a, b], [nw, nw2], [0.5, 0.5], 1e-6) for a, b in zip(ya, yb)])
+            us2 = timed(lambda: [ops.add_group_rmsnorm(r, y, [nw, nw2], 4, 1e-6, torch.bfloat16) for r, y in zip(rs, ya)])
+            by, by2 = T * W * (2 + 2 + 4), T * W * (8 + 2 + 4)
+            out(f"sum of two normed branches W{W} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
+                group_norm_us=round(us2, 2), group_norm_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))
+            # the left half: convolution with its state update, then norms over the whole of q and k, rotation, cache write
+            C = (Hl + G) * dd + G * dd
+            projs = [torch.randn(T, C, device=dev).to(torch.bfloat16) for _ in range(L)]
+            taps = torch.randn(K, C, device=dev) * 0.3
+            cstate = [torch.randn(R_, K - 1, C, device=dev) for _ in range(L)]
+            us = timed(lambda: [(ops.causal_conv(y, 0, taps, c, batch, torch.float32), ops.conv_state_update(y, 0, c, batch))
+                                for y, c in zip(projs, cstate)])
+            by = T * C * (2 + 4) + R_ * (K - 1) * C * 8
+            out(f"convolution on q, k, v taps{K} C{C} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3))
+            convd = [torch.randn(T, C, device=dev) for _ in range(L)]
+            blocks = -(-T // page) + 1
+            kvc = [torch.zeros(blocks, 2, G, page, dd, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+            slots = torch.arange(T, dtype=torch.int32, device=dev)
+            qn, kn, qn1 = torch.ones(Hl * dd, device=dev), torch.ones(G * dd, device=dev), torch.ones(dd, device=dev)
+            fac = torch.full((Hl,), 0.1, device=dev)
+            us = timed(lambda: [ops.attention_prepare(x, kv, qn, kn, 1e-6, freq, dd // 2, True, batch.positions, slots, fac,
+                                                      Hl, G, dd, dd, dd, norm_whole=True, out_dtype=torch.bfloat16)
+                                for x, kv in zip(convd, kvc)])
+            us2 = timed(lambda: [ops.attention_prepare(x, kv, qn1, qn1, 1e-6, freq, dd // 2, True, batch.positions, slots,
+                                                       fac, Hl, G, dd, dd, dd) for x, kv in zip(projs, kvc)])
+            by, by2 = T * C * (4 + 2), T * C * (2 + 2)
+            out(f"before attention, norms over all of q and k, H{Hl} G{G} d{dd} T{T}", us,
+                frac=round(by / us / 1e3 / pk["hbm_gbs"], 3), per_head_us=round(us2, 2),
+                per_head_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))
+            # the right half: silu on q, k, v; the norm over all heads with a sigmoid gate
+            pr = [torch.randn(T, 4 * Hl * dd, device=dev).to(torch.bfloat16) for _ in range(L)]
+            f0 = rotary_frequencies(0, 10.0).to(dev)
+            us = timed(lambda: [ops.retention_prepare(x, 0, Hl * dd, f0, 0, batch.positions, Hl, dd, 1.0, silu=True,
+                                                      v_off=2 * Hl * dd, dv=dd) for x in pr])
+            us2 = timed(lambda: [ops.retention_prepare(x, 0, Hl * dd, freq, dd, batch.positions, Hl, dd, 0.1) for x in pr])
+            by, by2 = T * 3 * Hl * dd * (2 + 4), T * 2 * Hl * dd * (2 + 4)
+            out(f"lightning prepare (silu on q, k, v) H{Hl} d{dd} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
+                retention_us=round(us2, 2), retention_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))
+            os_ = [torch.randn(T, Hl, dd, device=dev) for _ in range(L)]
+            gs = [torch.randn(T, Hl * dd, device=dev).to(torch.bfloat16) for _ in range(L)]
+            nwl = torch.ones(Hl * dd, device=dev)
+            us = timed(lambda: [ops.head_norm_gate(o, g, nwl, 1e-6, torch.bfloat16, whole=True, gate_kind="sigmoid")
+                                for o, g in zip(os_, gs)])
+            us2 = timed(lambda: [ops.head_norm_gate(o, g, nwl[:dd], 1e-6, torch.bfloat16) for o, g in zip(os_, gs)])
+            by = T * Hl * dd * (4 + 2 + 2)
+            out(f"norm over all heads and sigmoid gate H{Hl} dv{dd} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
+                per_head_us=round(us2, 2), per_head_frac=round(by / us2 / 1e3 / pk["hbm_gbs"], 3))
+            # the experts' rows, each times its weight, in expert order, beside the plain gather
+            E, top = 32, 4
+            xs = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(L)]
+            ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(T)]).to(torch.int32).contiguous()
+            wts = torch.rand(T, top, device=dev)
+            sp, pp, tiles = ops.moe_align(ids, E, 128 if T > 64 else 32)
+            us = timed(lambda: [ops.moe_scaled_rows(x, sp, top, wts, T * top) for x in xs])
+            by = T * top * W * (2 + 2)
+            out(f"experts' rows times their weights W{W} T{T} top{top}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3))
+        # causal attention with a sink and a gate per head beside the same kernels without: 64 single tokens at
+        # context 4,096, and a prompt of 4,096
+        for T, B in ((64, 64), (4096, 1)):
+            ctx = 4096
+            blocks = -(-ctx // page)
+            kvs = [torch.randn(B * blocks, 2, G, page, dd, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(B * blocks, dtype=torch.int32, device=dev).view(B, blocks).contiguous()
+            q = (torch.randn(T, Hh * dd, device=dev) * dd ** -0.5).to(torch.bfloat16)
+            req = (torch.arange(T, device=dev) // (T // B)).to(torch.int32)
+            pos = (torch.arange(T, device=dev) % (T // B) + (ctx - T // B)).to(torch.int32)
+            o = torch.empty(T, Hh * dd, dtype=torch.bfloat16, device=dev)
+            sink = torch.zeros(Hh, device=dev)
+            gate = torch.randn(T, Hh, device=dev).to(torch.bfloat16)
+            res = {}
+            for with_sink in (True, False):
+                more = dict(sink=sink, gate=gate) if with_sink else {}
+                if B > 1:
+                    splits = ops.decode_splits(T, G * (-(-(Hh // G) // 8)), ctx)
+                    res[with_sink] = timed(lambda: [ops.decode_attention(q, Hh * dd, o, kv, bt, None, T, req, pos, Hh, G, dd, 0,
+                                                                         1.0, splits, **more) for kv in kvs])
+                else:
+                    t64 = torch.tensor([(k, min(64, T - k), 0) for k in range(0, T, 64)], dtype=torch.int32, device=dev)
+                    res[with_sink] = timed(lambda: [ops.prefill_attention(q, Hh * dd, o, kv, bt, t64, pos, Hh, G, dd, 0, 1.0,
+                                                                          **more) for kv in kvs])
+            seen = sum(int(p) + 1 for p in pos.tolist())
+            by = B * ctx * G * 2 * dd * 2
+            fl = Hh * 4 * dd * seen
+            out(f"attention with a sink and a gate, H{Hh} G{G} d{dd}, {B} requests x {T // B} tokens", res[True],
+                without_us=round(res[False], 2), TFLOPs=round(fl / res[True] / 1e6, 2),
+                **({"frac_hbm": round(by / res[True] / 1e3 / pk["hbm_gbs"], 3),
+                    "without_frac_hbm": round(by / res[False] / 1e3 / pk["hbm_gbs"], 3)} if B > 1 else
+                   {"frac_flops": round(fl / res[True] / 1e6 / pk["bf16_tflops"], 3),
+                    "without_frac_flops": round(fl / res[False] / 1e6 / pk["bf16_tflops"], 3)}))
     if on("moe"):
         # the routed experts' two grouped products (32 experts of 1,024 at width 2,048, 4 choices) beside the dense
         # model's gate|up and down products of equal work: decode by bytes of weights read, prompts by FLOP/s
@@ -1182,14 +1426,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar", "rupulix", "mepatar"],
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar", "rupulix", "mepatar", "kasarax"],
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
                          "kernels: the hot kernels one by one; dizatar / rupulix: prefill and decode of the Dizatar / Rupulix design at "
                          "layer sizes of real models beside the dense model of equal width; mepatar: the same for "
-                         "the Mepatar design beside Rupulix")
-    ap.add_argument("--sizes", default="", help="--mode dizatar / rupulix / mepatar: comma-separated subset of w1024, w2048")
+                         "the Mepatar design beside Rupulix; kasarax: the same for the Kasarax design beside Mepatar")
+    ap.add_argument("--sizes", default="", help="--mode dizatar / rupulix / mepatar / kasarax: comma-separated subset of w1024, w2048")
     ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
-                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives, latent_attention, moe")
+                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives, latent_attention, moe, "
+                    "talking_attention, rupulix_rows, mepatar_rows, kasarax_rows")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--mode decode: tokens each request holds")
@@ -1212,6 +1457,8 @@ def main():
         return run_rupulix(args)
     if args.mode == "mepatar":
         return run_mepatar(args)
+    if args.mode == "kasarax":
+        return run_kasarax(args)
     return run_ours(args)
 
 
