@@ -1324,7 +1324,8 @@ def run_kernels(args):
             f0 = rotary_frequencies(0, 10.0).to(dev)
             us = timed(lambda: [ops.retention_prepare(x, 0, Hl * dd, f0, 0, batch.positions, Hl, dd, 1.0, silu=True,
                                                       v_off=2 * Hl * dd, dv=dd) for x in pr])
-            us2 = timed(lambda: [ops.retention_prepare(x, 0, Hl * dd, freq, dd, batch.positions, Hl, dd, 0.1) for x in pr])
+            fd = rotary_frequencies(dd, 10000.0).to(dev)
+            us2 = timed(lambda: [ops.retention_prepare(x, 0, Hl * dd, fd, dd, batch.positions, Hl, dd, 0.1) for x in pr])
             by, by2 = T * 3 * Hl * dd * (2 + 4), T * 2 * Hl * dd * (2 + 4)
             out(f"lightning prepare (silu on q, k, v) H{Hl} d{dd} T{T}", us, frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
                 retention_us=round(us2, 2), retention_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))

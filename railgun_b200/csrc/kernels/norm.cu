@@ -398,7 +398,9 @@ __global__ void __launch_bounds__(256) norm_sum_kernel(NormSumArgs a, float eps,
     float acc[NS_KEEP];
 #pragma unroll
     for (int j = 0; j < NS_KEEP; ++j) acc[j] = 0.f;
-    for (int b = 0; b < a.n; ++b) {
+#pragma unroll
+    for (int b = 0; b < NS_MAX; ++b) {
+        if (b >= a.n) break;
         const P* y = reinterpret_cast<const P*>(a.y[b]) + base;
         float keep[NS_KEEP];
         float ss = 0.f;
@@ -429,6 +431,82 @@ __global__ void __launch_bounds__(256) norm_sum_kernel(NormSumArgs a, float eps,
     }
 }
 
+// The same with 16-byte loads: a thread holds NV pieces of 8 bfloat16 (or 4 float) numbers of every input, rows and
+// weights start on 16-byte boundaries, H is a multiple of the piece.
+template <typename P, int NV>
+__global__ void __launch_bounds__(256) norm_sum_vec_kernel(NormSumArgs a, float eps, float* __restrict__ out, int H) {
+    constexpr int PIECE = 16 / sizeof(P);
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const size_t base = (size_t)blockIdx.x * H;
+    const int pieces = H / PIECE;
+    float acc[NV][PIECE];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < PIECE; ++e) acc[j][e] = 0.f;
+#pragma unroll
+    for (int b = 0; b < NS_MAX; ++b) {
+        if (b >= a.n) break;
+        const P* y = reinterpret_cast<const P*>(a.y[b]) + base;
+        float keep[NV][PIECE];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < pieces) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)i * PIECE);
+                if (sizeof(P) == 2) {
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < PIECE / 2; ++e) {
+                        const float2 f = __bfloat1622float2(h2[e]);
+                        keep[j][2 * e] = f.x;
+                        keep[j][2 * e + 1] = f.y;
+                    }
+                } else {
+                    const float* f = reinterpret_cast<const float*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < PIECE; ++e) keep[j][e] = f[e];
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < PIECE; ++e) keep[j][e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < PIECE; ++e) ss += keep[j][e] * keep[j][e];
+        }
+        ss = block_sum(ss, scratch);
+        const float f = rsqrtf(ss / (float)H + eps) * a.c[b];
+        const float* w = a.w[b];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < pieces) {
+#pragma unroll
+                for (int e4 = 0; e4 < PIECE / 4; ++e4) {
+                    const float4 wv = *reinterpret_cast<const float4*>(w + (size_t)i * PIECE + 4 * e4);
+                    acc[j][4 * e4] += keep[j][4 * e4] * f * wv.x;
+                    acc[j][4 * e4 + 1] += keep[j][4 * e4 + 1] * f * wv.y;
+                    acc[j][4 * e4 + 2] += keep[j][4 * e4 + 2] * f * wv.z;
+                    acc[j][4 * e4 + 3] += keep[j][4 * e4 + 3] * f * wv.w;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < pieces) {
+#pragma unroll
+            for (int e4 = 0; e4 < PIECE / 4; ++e4)
+                *reinterpret_cast<float4*>(out + base + (size_t)i * PIECE + 4 * e4) =
+                    make_float4(acc[j][4 * e4], acc[j][4 * e4 + 1], acc[j][4 * e4 + 2], acc[j][4 * e4 + 3]);
+        }
+    }
+}
+
 // ys, ws: n pointers each (rows of H numbers of type `dtype`; weights [H] float); cs: n constants.
 extern "C" int rg_norm_sum(const void* const* ys, const float* const* ws, const float* cs, int n, int dtype, float eps,
                            float* out, int T, int H, void* stream) {
@@ -436,13 +514,28 @@ extern "C" int rg_norm_sum(const void* const* ys, const float* const* ws, const 
     if (n < 1 || n > NS_MAX || H < 1) return RG_ERR_UNSUPPORTED;
     NormSumArgs a;
     a.n = n;
+    uintptr_t bits = (uintptr_t)out;
     for (int b = 0; b < NS_MAX; ++b) {
         a.y[b] = b < n ? ys[b] : nullptr;
         a.w[b] = b < n ? ws[b] : nullptr;
         a.c[b] = b < n ? cs[b] : 0.f;
+        if (b < n) bits |= (uintptr_t)ys[b] | (uintptr_t)ws[b];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int piece = dtype == RG_DTYPE_BF16 ? 8 : 4;
+    if ((bits & 15) == 0 && H % piece == 0 && H / piece <= 4 * 256 && (dtype == RG_DTYPE_BF16 || dtype == RG_DTYPE_F32)) {
+        const int pieces = H / piece;
+        const int nv = pieces <= 256 ? 1 : (pieces <= 512 ? 2 : 4);
+        int threads = ((pieces + nv - 1) / nv + 31) / 32 * 32;
+        if (threads < 32) threads = 32;
+#define RG_NSV(P, NV) return rg_launch(norm_sum_vec_kernel<P, NV>, dim3(T), dim3(threads), 0, s, 1, a, eps, out, H)
+        if (dtype == RG_DTYPE_BF16) { if (nv == 1) RG_NSV(bf16, 1); if (nv == 2) RG_NSV(bf16, 2); RG_NSV(bf16, 4); }
+        if (nv == 1) RG_NSV(float, 1);
+        if (nv == 2) RG_NSV(float, 2);
+        RG_NSV(float, 4);
+#undef RG_NSV
     }
     const int threads = H >= 2048 ? 256 : (H >= 512 ? 128 : 64);
-    cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RG_DTYPE_BF16) return rg_launch(norm_sum_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, a, eps, out, H);
     if (dtype == RG_DTYPE_F32) return rg_launch(norm_sum_kernel<float>, dim3(T), dim3(threads), 0, s, 1, a, eps, out, H);
     return RG_ERR_UNSUPPORTED;

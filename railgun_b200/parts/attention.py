@@ -291,9 +291,18 @@ class NormedAttention(Mixer):
         self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
                                         lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
 
-    def forward(self, x, batch, cache, writes=True):
+    def input_weight(self):
+        """The matrix of this mixer's first product, for a wrapper that computes the first products of several
+        mixers that read the same rows as one (None: the product has a bias and stays here)."""
+        return self.w_qkv if self.b_qkv is None else None
+
+    def adopt_input_weight(self, view):
+        self.w_qkv = view
+
+    def forward(self, x, batch, cache, writes=True, proj=None):
         H, G, d, dv, D, C = self.H, self.G, self.d, self.dv, self.D, self.C
-        proj = ops.linear(x, self.w_qkv, bias=self.b_qkv)                     # [T, q | k | v (| gate)]
+        if proj is None:
+            proj = ops.linear(x, self.w_qkv, bias=self.b_qkv)                 # [T, q | k | v (| gate)]
         pages = cache.parts[0] if self.K > 1 else cache
         qkv = proj if proj.shape[1] == C else proj[:, :C]
         if self.K >= 1:

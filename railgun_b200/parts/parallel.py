@@ -14,7 +14,9 @@ tuple of needs, one per branch.
 With ``out_norms`` every branch's output is RMS-normed over the width with a
 weight of its own before the sum, sum_b c_b norm_b(branch_b(x)): the branches
 are then any mixers, run one after the other through their ``forward``, and
-the norms, constants and sum are one kernel (ops.norm_sum, 32-bit).
+the norms, constants and sum are one kernel (ops.norm_sum, 32-bit); branches
+that hand out the matrix of their first product (``input_weight()``) get that
+product from here, one for all of them.
 """
 from __future__ import annotations
 
@@ -75,6 +77,17 @@ class Parallel(Mixer):
                 raise ValueError("'parallel' with out_norms: one norm per branch, four branches at most")
             self.out_norms = [tensors.get(prefix + n, torch.float32).contiguous() for n in p["out_norms"]]
             self.eps = float(p["eps"])
+            # branches that hand out the matrix of their first product get that product from here: one product
+            # over the matrices stacked by rows, of which every branch reads its columns
+            self.stacked, self.in_cols = None, []
+            ws = [part.input_weight() if hasattr(part, "input_weight") else None for part in self.parts]
+            if len(ws) > 1 and all(w is not None for w in ws):
+                self.stacked = torch.cat(ws, dim=0).contiguous()
+                at = 0
+                for part, w in zip(self.parts, ws):
+                    part.adopt_input_weight(self.stacked[at:at + w.shape[0]])
+                    self.in_cols.append((at, at + w.shape[0]))
+                    at += w.shape[0]
             return
         for part in self.parts:
             if not all(hasattr(part, a) for a in ("mix", "w_o", "w_in")):
@@ -97,7 +110,12 @@ class Parallel(Mixer):
 
     def forward(self, x, batch, cache, writes=True):
         if self.out_norms is not None:
-            ys = [part.forward(x, batch, view, writes) for part, view in zip(self.parts, self._views(cache))]
+            if self.stacked is not None:
+                proj = ops.linear(x, self.stacked)
+                ys = [part.forward(x, batch, view, writes, proj=proj[:, a:b])
+                      for part, view, (a, b) in zip(self.parts, self._views(cache), self.in_cols)]
+            else:
+                ys = [part.forward(x, batch, view, writes) for part, view in zip(self.parts, self._views(cache))]
             return ops.norm_sum(ys, self.out_norms, self.scales, self.eps)
         T = x.shape[0]
         proj = ops.linear(x, self.w_in)

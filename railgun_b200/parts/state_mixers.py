@@ -88,9 +88,18 @@ class Retention(Mixer):
         self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
                                         lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
 
-    def forward(self, x, batch, cache, writes=True):
+    def input_weight(self):
+        """The matrix of the first product, for a wrapper that computes the first products of several mixers that
+        read the same rows as one."""
+        return self.w_in
+
+    def adopt_input_weight(self, view):
+        self.w_in = view
+
+    def forward(self, x, batch, cache, writes=True, proj=None):
         H, d, dv = self.H, self.d, self.dv
-        proj = ops.linear(x, self.w_in)                                      # [T, q | k | v | gate]
+        if proj is None:
+            proj = ops.linear(x, self.w_in)                                  # [T, q | k | v | gate]
         if self.silu:
             q, k, v = ops.retention_prepare(proj, 0, H * d, self.freq, self.rot_dims, batch.positions, H, d,
                                             self.k_scale, silu=True, v_off=2 * H * d, dv=dv)
