@@ -8,7 +8,7 @@ factors that step every 1, 7 and 50 positions and none; left halves with
 convolutions of 1 to 5 taps, rotation of none, part and all of a head;
 right halves with one head and several, decays from 0.5 to 1; one, some and
 all experts chosen; logit scales on both sides of one; sizes that are no
-multiple of 8.
+multiple of 8, and a width that is no multiple of 4.
 
 Weights are random but not all alike: the one-plus norm weights well away
 from zero, plain norm weights away from one, biases and sinks that matter,
@@ -92,7 +92,16 @@ CASE_D = dict(
             layer(attention(4, 4, 32, 32, coef=0.2, every=128), moe(12, 2, 32)),
             layer(parallel(left(2, 1, 128, 64, 2, dims=64, base=5000.0), right(2, 64, 64, [0.98, 1.0])), moe(8, 3, 48))])
 
-CASES = {"A": (CASE_A, 3, 8), "B": (CASE_B, 5, 16), "C": (CASE_C, 7, 32), "D": (CASE_D, 9, 16)}    # config, seed, page
+# E: a width and a vocabulary that are multiples of neither 8 nor 4 (rows that start off 16-byte boundaries); head
+#    sizes of 10 and 6; an attention layer last; seven taps.
+CASE_E = dict(
+    architecture="Kasarax", width=38, vocab=77, norm=dict(eps=1e-5), logit_scale=1.7,
+    layers=[layer(parallel(left(2, 2, 10, 6, 7, dims=4, base=50.0), right(3, 6, 10, [0.93, 0.99, 0.9999])), dense(30)),
+            layer(parallel(left(4, 1, 6, 10, 1, dims=6, base=9.0), right(1, 10, 6, [0.97])), moe(5, 2, 9)),
+            layer(attention(5, 5, 6, 10, coef=0.7, every=11), moe(2, 1, 14))])
+
+CASES = {"A": (CASE_A, 3, 8), "B": (CASE_B, 5, 16), "C": (CASE_C, 7, 32), "D": (CASE_D, 9, 16),
+         "E": (CASE_E, 11, 4)}                                                                # config, seed, page
 
 _made: dict = {}
 _plain: dict = {}

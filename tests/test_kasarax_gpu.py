@@ -323,7 +323,7 @@ def test_experts_alone(name, layer, dtype):
 # ---- the model through the step function ---------------------------------------------------------------
 
 LENGTHS = {"A": [1, 2, 9, 12, 40, 77, 150, 64], "B": [1, 3, 17, 64, 100, 33], "C": [1, 6, 10, 33, 90, 65],
-           "D": [2, 131, 260, 400, 55, 129, 181]}
+           "D": [2, 131, 260, 400, 55, 129, 181], "E": [1, 2, 5, 23, 70, 41]}
 PORTIONS = {"D": (130, 2, 64, 7, 128, 3, 65, 2, 33, 129)}
 MIXED = {"D": (5, 1, 2, 70, 1, 1, 3, 140, 1, 2, 128, 17)}
 TAIL = {"D": 140, "B": 60}                          # the query factor's steps at 50, 100 and 128 fall on decoded tokens
@@ -418,7 +418,7 @@ def test_replay_matches_plain(name, dtype, mode, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
 def test_every_token_decoded_alone_matches_whole_prompts(name, dtype, tmp_path):
     """Token-by-token decoding from the first token on (through the decode graphs and with graphs off): states
     and convolution tails that start from nothing, query factors that step between decoded tokens."""
