@@ -153,7 +153,8 @@ def plain_sink_rows(q, k, v, pos, sink, gate):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,d,dv,page", [(4, 2, 16, 8, 8), (6, 2, 112, 80, 16), (3, 3, 24, 40, 16), (2, 1, 16, 16, 4),
                                            (8, 8, 32, 32, 32), (5, 1, 12, 20, 16), (4, 4, 64, 64, 16),
-                                           (16, 2, 128, 128, 64), (12, 1, 64, 32, 16)])
+                                           (16, 2, 128, 128, 64), (12, 1, 64, 32, 16), (4, 2, 160, 96, 16),
+                                           (2, 1, 256, 64, 16), (6, 2, 144, 144, 8), (3, 1, 40, 200, 16)])
 def test_sink_attention_kernels_alone(H, G, d, dv, page, dtype):
     """Head 0 of the last query points at one key (the first, at page borders, far back, the last); head 1 has a
     sink so large that most of its weight goes nowhere, head 2 (if there is one) a sink that does not matter; the
